@@ -1,0 +1,449 @@
+// C-ABI entry points of the direct operators: validation (same conditions and error
+// classes as the reference's op::cuda functions, rejected before any write) and dispatch to
+// the sm_100a kernels. No entry point allocates; scratch is the caller's.
+#include "abi_util.cuh"
+#include "kernels.cuh"
+#include "smallm_gemm.cuh"
+
+#include <cmath>
+#include <limits>
+
+namespace ei {
+
+thread_local std::string g_last_error;
+
+namespace {
+
+int checked_int(size_t value) {
+  if (!value || value > size_t(std::numeric_limits<int>::max()))
+    throw std::invalid_argument("CUDA execution extent must be positive and fit int");
+  return int(value);
+}
+
+template <typename View>
+size_t numel(const View& v) {
+  size_t count = 1;
+  for (size_t extent : v.shape) count *= extent;
+  return count;
+}
+
+template <typename View>
+bool contiguous(const View& v) {
+  if (!numel(v)) return true;
+  size_t expected = 1;
+  constexpr size_t rank = sizeof(v.shape) / sizeof(v.shape[0]);
+  for (size_t axis = rank; axis-- > 0;) {
+    if (v.shape[axis] != 1 && v.stride[axis] != expected) return false;
+    expected *= v.shape[axis];
+  }
+  return true;
+}
+
+template <typename View>
+void require_dense(const View& v) {
+  if (!v.data || !numel(v) || !contiguous(v))
+    throw std::invalid_argument("CUDA execution requires a nonempty contiguous view");
+}
+
+void require_heads(const ei_view3& v) {
+  if (!v.data || !numel(v) || v.stride[2] != 1 || v.stride[1] != v.shape[2] ||
+      v.stride[0] < v.shape[1] * v.shape[2])
+    throw std::invalid_argument("CUDA attention/RoPE requires contiguous heads within each row");
+  checked_int(v.shape[0]);
+  checked_int(v.shape[1]);
+  checked_int(v.shape[2]);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+cudaStream_t stream_of(const ei_context* ctx) {
+  if (!ctx) throw std::invalid_argument("execution context is null");
+  return static_cast<cudaStream_t>(ctx->stream);
+}
+
+size_t smem_limit_of(const ei_context* ctx) {
+  return ctx->shared_memory_limit ? ctx->shared_memory_limit : size_t(227) * 1024;
+}
+
+// Rows are processed 16 at a time; each group streams the weights once.
+template <typename Launch>
+void for_row_groups(size_t rows, Launch&& body) {
+  for (size_t first = 0; first < rows; first += 16) body(first, std::min<size_t>(16, rows - first));
+}
+
+}  // namespace
+}  // namespace ei
+
+using namespace ei;
+
+extern "C" {
+
+const char* ei_last_error(void) { return g_last_error.c_str(); }
+const char* ei_version(void) { return "edge_infer_b200 0.1 (sm_100a)"; }
+
+ei_status ei_prepare_execution_context(void* stream, ei_context* out) {
+  return guarded([&] {
+    if (!out) throw std::invalid_argument("context output is null");
+    ei_context ctx{};
+    ctx.stream = stream;
+    EI_CUDA(cudaGetDevice(&ctx.device));
+    int value = 0;
+    EI_CUDA(cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, ctx.device));
+    ctx.multiprocessors = value;
+    EI_CUDA(cudaDeviceGetAttribute(&value, cudaDevAttrMaxThreadsPerBlock, ctx.device));
+    ctx.max_threads_per_block = value;
+    EI_CUDA(cudaDeviceGetAttribute(&value, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx.device));
+    ctx.shared_memory_limit = size_t(value);
+    *out = ctx;
+  });
+}
+
+ei_status ei_prepare_dense_bf16(ei_view2 weight, ei_view1 bias, ei_dense_weight* out) {
+  return guarded([&] {
+    const int input = checked_int(weight.shape[0]), output = checked_int(weight.shape[1]);
+    if (!out || !weight.data ||
+        (bias.data && (bias.shape[0] != weight.shape[1] || (bias.shape[0] != 1 && bias.stride[0] != 1))))
+      throw std::invalid_argument("Invalid direct dense linear weight or bias");
+    ei_dense_weight prepared{};
+    prepared.data = weight.data;
+    prepared.bias = bias.data;
+    prepared.input_features = input;
+    prepared.output_features = output;
+    if (weight.stride[0] == 1 && weight.stride[1] >= weight.shape[0]) {
+      prepared.operation = 1;
+      prepared.leading_dimension = checked_int(weight.stride[1]);
+    } else if (weight.stride[1] == 1 && weight.stride[0] >= weight.shape[1]) {
+      prepared.operation = 0;
+      prepared.leading_dimension = checked_int(weight.stride[0]);
+    } else {
+      throw std::invalid_argument("Direct dense linear supports row-major or transposed matrix views");
+    }
+    *out = prepared;
+  });
+}
+
+ei_status ei_prepare_awq_bf16(ei_view2 qweight, ei_view2 scales, ei_view2 zeros, size_t group_size,
+                              size_t input_features, ei_view1 bias, ei_awq_weight* out) {
+  return guarded([&] {
+    require_dense(qweight);
+    require_dense(scales);
+    require_dense(zeros);
+    const int input = checked_int(input_features), output = checked_int(qweight.shape[0]);
+    const int group = checked_int(group_size), padded = checked_int(scales.shape[1]);
+    if (!out || input_features % group_size || qweight.shape[1] != (input_features + 7) / 8 ||
+        scales.shape[0] != qweight.shape[0] || scales.shape[1] < input_features / group_size ||
+        zeros.shape[0] != qweight.shape[0] || zeros.shape[1] != (input_features / group_size + 7) / 8 ||
+        (bias.data && (bias.shape[0] != qweight.shape[0] || (bias.shape[0] != 1 && bias.stride[0] != 1))))
+      throw std::invalid_argument("Direct AWQ linear requires N-major packed weights, scales and zeros");
+    *out = ei_awq_weight{static_cast<const int32_t*>(qweight.data), scales.data,
+                         static_cast<const int32_t*>(zeros.data), bias.data, input, output, group, padded};
+  });
+}
+
+size_t ei_linear_scratch_bytes(size_t rows, size_t input_features, size_t output_features) {
+  (void)input_features;
+  // Worst case split of the input features over blocks: 16 FP32 partial copies of a 16-row group.
+  return size_t(16) * std::min<size_t>(rows, 16) * output_features * sizeof(float);
+}
+
+ei_status ei_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_dense_weight* weight, ei_view2 output,
+                         void* scratch, size_t scratch_bytes) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_dense(input);
+    require_dense(output);
+    checked_int(input.shape[0]);
+    if (!weight || !weight->data || input.shape[1] != size_t(weight->input_features) ||
+        output.shape[0] != input.shape[0] || output.shape[1] != size_t(weight->output_features))
+      throw std::invalid_argument("Direct dense linear input/output dimensions or handle are invalid");
+    const int K = weight->input_features, N = weight->output_features;
+    const bool fast_layout = weight->operation == 1 && aligned16(weight->data) && weight->leading_dimension % 8 == 0 &&
+                             aligned16(input.data);
+    for_row_groups(input.shape[0], [&](size_t first, size_t rows) {
+      const bf16* x = static_cast<const bf16*>(input.data) + first * K;
+      bf16* out = static_cast<bf16*>(output.data) + first * N;
+      GemmPlan plan;
+      if (fast_layout)
+        plan = plan_gemm(false, int(rows), N, K, kEpiStore, ctx->multiprocessors, smem_limit_of(ctx), scratch != nullptr);
+      if (plan.fast && plan.ksplit > 1 && scratch_bytes < size_t(plan.ksplit) * rows * N * sizeof(float))
+        plan.fast = false;
+      if (plan.fast) {
+        GemmParams p{};
+        p.x = x; p.x_stride = K; p.M = int(rows); p.K = K; p.N = N;
+        p.w = static_cast<const bf16*>(weight->data); p.ldw = weight->leading_dimension;
+        p.bias = static_cast<const bf16*>(weight->bias);
+        p.out = out; p.out_stride = N;
+        p.ksplit = plan.ksplit;
+        p.epilogue = plan.ksplit > 1 ? kEpiPartial : kEpiStore;
+        p.partial = static_cast<float*>(scratch);
+        launch_gemm(plan, false, p, stream, false);
+        if (plan.ksplit > 1) {
+          splitk_store_kernel<<<std::min(1024, (int(rows) * N + 255) / 256), 256, 0, stream>>>(
+              p.partial, plan.ksplit, int(rows), N, p.bias, out, N);
+          check_launch();
+        }
+      } else {
+        const long long stride_k = weight->operation == 1 ? 1 : weight->leading_dimension;
+        const long long stride_n = weight->operation == 1 ? weight->leading_dimension : 1;
+        const size_t count = rows * size_t(N);
+        dense_generic_kernel<<<unsigned(std::min<size_t>((count + 255) / 256, size_t(ctx->multiprocessors) * 32)), 256, 0,
+                               stream>>>(x, K, static_cast<const bf16*>(weight->data), stride_k, stride_n,
+                                         static_cast<const bf16*>(weight->bias), out, N, int(rows), N, K);
+        check_launch();
+      }
+    });
+  });
+}
+
+ei_status ei_awq_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_awq_weight* weight, ei_view2 output,
+                             void* scratch, size_t scratch_bytes) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_dense(input);
+    require_dense(output);
+    checked_int(input.shape[0]);
+    if (!weight || !weight->qweight || !weight->scales || !weight->zeros ||
+        input.shape[1] != size_t(weight->input_features) || output.shape[0] != input.shape[0] ||
+        output.shape[1] != size_t(weight->output_features))
+      throw std::invalid_argument("Direct AWQ linear input/output dimensions are invalid");
+    const int K = weight->input_features, N = weight->output_features;
+    const bool fast_layout = weight->group_size == 128 && aligned16(weight->qweight) && aligned16(input.data);
+    for_row_groups(input.shape[0], [&](size_t first, size_t rows) {
+      const bf16* x = static_cast<const bf16*>(input.data) + first * K;
+      bf16* out = static_cast<bf16*>(output.data) + first * N;
+      GemmPlan plan;
+      if (fast_layout)
+        plan = plan_gemm(true, int(rows), N, K, kEpiStore, ctx->multiprocessors, smem_limit_of(ctx), scratch != nullptr);
+      if (plan.fast && plan.ksplit > 1 && scratch_bytes < size_t(plan.ksplit) * rows * N * sizeof(float))
+        plan.fast = false;
+      if (plan.fast) {
+        GemmParams p{};
+        p.x = x; p.x_stride = K; p.M = int(rows); p.K = K; p.N = N;
+        p.qweight = weight->qweight;
+        p.scales = static_cast<const bf16*>(weight->scales);
+        p.zeros = weight->zeros;
+        p.padded_groups = weight->padded_groups;
+        p.zero_stride = (K / 128 + 7) / 8;
+        p.bias = static_cast<const bf16*>(weight->bias);
+        p.out = out; p.out_stride = N;
+        p.ksplit = plan.ksplit;
+        p.epilogue = plan.ksplit > 1 ? kEpiPartial : kEpiStore;
+        p.partial = static_cast<float*>(scratch);
+        launch_gemm(plan, true, p, stream, false);
+        if (plan.ksplit > 1) {
+          splitk_store_kernel<<<std::min(1024, (int(rows) * N + 255) / 256), 256, 0, stream>>>(
+              p.partial, plan.ksplit, int(rows), N, p.bias, out, N);
+          check_launch();
+        }
+      } else {
+        const size_t count = rows * size_t(N);
+        awq_generic_kernel<<<unsigned(std::min<size_t>((count + 255) / 256, size_t(ctx->multiprocessors) * 32)), 256, 0,
+                             stream>>>(x, K, weight->qweight, static_cast<const bf16*>(weight->scales), weight->zeros,
+                                       static_cast<const bf16*>(weight->bias), out, N, int(rows), N, K,
+                                       weight->group_size, weight->padded_groups);
+        check_launch();
+      }
+    });
+  });
+}
+
+ei_status ei_add_bf16(const ei_context* ctx, ei_array a, ei_array b, ei_array out) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    if (a.size != b.size || a.size != out.size)
+      throw std::runtime_error("Add operator: input and output views must have the same size");
+    if (!a.size) return;
+    if (!a.data || !b.data || !out.data) throw std::invalid_argument("Add operator: null storage");
+    launch_add(static_cast<const bf16*>(a.data), static_cast<const bf16*>(b.data), static_cast<bf16*>(out.data),
+               a.size, stream);
+  });
+}
+
+ei_status ei_silu_multiply_bf16(const ei_context* ctx, ei_array gate, ei_array up, ei_array out) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    if (up.size != gate.size || out.size != gate.size)
+      throw std::runtime_error("SiLU multiply operator: input and output views must have the same size");
+    if (!gate.size) return;
+    if (gate.size > size_t(std::numeric_limits<int>::max()))
+      throw std::runtime_error("SiLU multiply CUDA view extent exceeds the kernel index range");
+    launch_silu_multiply(static_cast<const bf16*>(gate.data), static_cast<const bf16*>(up.data),
+                         static_cast<bf16*>(out.data), gate.size, stream);
+  });
+}
+
+ei_status ei_rms_norm_bf16(const ei_context* ctx, ei_array input, ei_array weight, ei_array out, size_t rows,
+                           size_t features, float epsilon) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    if (out.size != input.size)
+      throw std::runtime_error("RMSNorm operator: input and output views must have the same size");
+    if (!input.size) return;
+    if (!features || features > 10240)
+      throw std::runtime_error("RMSNorm CUDA feature_dim must be between 1 and 10240");
+    if (rows > size_t(std::numeric_limits<int>::max()))
+      throw std::runtime_error("RMSNorm CUDA row count exceeds the kernel index range");
+    if (input.size % features || input.size / features != rows || weight.size != features)
+      throw std::runtime_error("RMSNorm CUDA view extents do not match rows and feature_dim");
+    launch_rms_norm(static_cast<const bf16*>(input.data), static_cast<const bf16*>(weight.data),
+                    static_cast<bf16*>(out.data), rows, features, epsilon, stream, false);
+  });
+}
+
+ei_status ei_gather_bf16(const ei_context* ctx, ei_view1 ids, ei_view2 table, ei_view2 out) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_dense(ids);
+    require_dense(table);
+    require_dense(out);
+    if (out.shape[0] != ids.shape[0] || out.shape[1] != table.shape[1])
+      throw std::invalid_argument("Direct gather input/output shapes differ");
+    launch_gather(static_cast<const uint32_t*>(ids.data), static_cast<const bf16*>(table.data),
+                  static_cast<bf16*>(out.data), out.shape[0], table.shape[1], table.shape[0], ctx->multiprocessors,
+                  stream);
+  });
+}
+
+ei_status ei_rope_precomputed_bf16(const ei_context* ctx, ei_view3 input, ei_view2 table, size_t offset,
+                                   const size_t* offsets, const int* pingpong) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_heads(input);
+    require_dense(table);
+    if (table.shape[1] != input.shape[2] || input.shape[2] % 2 ||
+        input.shape[2] / 2 > size_t(ctx->max_threads_per_block ? ctx->max_threads_per_block : 1024))
+      throw std::invalid_argument("Direct cached RoPE has incompatible cache or offsets");
+    if (!offsets && (offset > table.shape[0] || input.shape[0] > table.shape[0] - offset))
+      throw std::out_of_range("Direct cached RoPE positions exceed table capacity");
+    launch_rope(static_cast<bf16*>(input.data), input.shape[0], input.shape[1], input.shape[2], input.stride[0],
+                static_cast<const float*>(table.data), table.stride[0], offset, offsets, pingpong, stream);
+  });
+}
+
+ei_status ei_build_rope_table(float* host_table, size_t max_positions, size_t head_dim, float theta) {
+  return guarded([&] {
+    if (!host_table || !max_positions || !head_dim || head_dim % 2 || !std::isfinite(theta) || theta <= 0.0f)
+      throw std::invalid_argument("RoPE table requires positive extents, an even head width and a positive theta");
+    for (size_t pos = 0; pos < max_positions; ++pos)
+      for (size_t i = 0; i < head_dim / 2; ++i) {
+        const float frequency = 1.0f / std::pow(theta, 2.0f * static_cast<float>(i) / static_cast<float>(head_dim));
+        const float angle = static_cast<float>(pos) * frequency;
+        host_table[pos * head_dim + 2 * i] = std::sin(angle);
+        host_table[pos * head_dim + 2 * i + 1] = std::cos(angle);
+      }
+  });
+}
+
+ei_status ei_store_kv_bf16(const ei_context* ctx, ei_view2 source, ei_view2 capacity, size_t offset,
+                           const size_t* device_offset) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_dense(source);
+    require_dense(capacity);
+    if (source.shape[1] != capacity.shape[1] || offset > capacity.shape[0] ||
+        source.shape[0] > capacity.shape[0] - offset)
+      throw std::invalid_argument("Direct KV store source or offset exceeds cache capacity");
+    launch_store_kv(static_cast<const bf16*>(source.data), static_cast<bf16*>(capacity.data), source.shape[0],
+                    source.shape[1], capacity.shape[0], offset, device_offset, ctx->multiprocessors, stream);
+  });
+}
+
+size_t ei_attention_scratch_bytes(size_t q_rows, size_t query_heads, size_t head_dim, size_t kv_length) {
+  (void)head_dim;
+  return attention_scratch_bytes(q_rows, query_heads, kv_length);
+}
+
+static void run_attention(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view3 v, ei_view3 out, size_t offset,
+                          const int32_t* device_offset, void* scratch, size_t scratch_bytes) {
+  cudaStream_t stream = stream_of(ctx);
+  require_heads(q);
+  require_heads(k);
+  require_heads(v);
+  require_heads(out);
+  if (k.shape[0] != v.shape[0] || k.shape[1] != v.shape[1] || k.shape[2] != v.shape[2] ||
+      q.shape[0] != out.shape[0] || q.shape[1] != out.shape[1] || q.shape[2] != out.shape[2] ||
+      q.shape[2] != k.shape[2] || q.shape[1] % k.shape[1] || q.shape[2] > 1024)
+    throw std::invalid_argument("CUDA attention query, KV and output shapes are incompatible");
+  if (!device_offset && (offset > k.shape[0] || q.shape[0] > k.shape[0] - offset))
+    throw std::invalid_argument("Direct prefill attention offset exceeds live KV extent");
+  const size_t group = q.shape[1] / k.shape[1];
+  if (q.shape[2] != 128 || q.shape[0] * group > 112 || k.stride[0] != v.stride[0] || !aligned16(q.data) ||
+      !aligned16(k.data) || !aligned16(v.data) || !aligned16(out.data) || (q.stride[0] * 2) % 16 ||
+      (k.stride[0] * 2) % 16 || (out.stride[0] * 2) % 16)
+    throw std::invalid_argument(
+        "Verify attention supports head_dim 128, rows * (heads / kv_heads) <= 112 and 16-byte aligned rows");
+  const size_t length = device_offset ? k.shape[0] : offset + q.shape[0];
+  if (!scratch || scratch_bytes < attention_scratch_bytes(q.shape[0], q.shape[1], length))
+    throw std::invalid_argument("Verify attention scratch capacity is insufficient");
+  AttentionParams p{};
+  p.q = static_cast<const bf16*>(q.data);
+  p.q_stride = int(q.stride[0]);
+  p.k = static_cast<const bf16*>(k.data);
+  p.v = static_cast<const bf16*>(v.data);
+  p.kv_stride = int(k.stride[0]);
+  p.rows = int(q.shape[0]);
+  p.heads = int(q.shape[1]);
+  p.kv_heads = int(k.shape[1]);
+  p.capacity = int(k.shape[0]);
+  p.device_offset = device_offset;
+  p.host_offset = int(offset);
+  p.chunk = attention_chunk_for(length);
+  p.max_splits = int((length + p.chunk - 1) / p.chunk);
+  p.scratch = static_cast<float*>(scratch);
+  p.out = static_cast<bf16*>(out.data);
+  p.out_stride = int(out.stride[0]);
+  launch_verify_attention(p, stream, false);
+}
+
+ei_status ei_attention_prefill_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view3 v, ei_view3 out,
+                                    size_t offset, void* scratch, size_t scratch_bytes) {
+  return guarded([&] { run_attention(ctx, q, k, v, out, offset, nullptr, scratch, scratch_bytes); });
+}
+
+ei_status ei_attention_verify_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k_capacity, ei_view3 v_capacity,
+                                   ei_view3 out, const int32_t* device_offset, void* scratch,
+                                   size_t scratch_bytes) {
+  return guarded([&] {
+    if (!device_offset) throw std::invalid_argument("Verify attention requires a device offset");
+    run_attention(ctx, q, k_capacity, v_capacity, out, 0, device_offset, scratch, scratch_bytes);
+  });
+}
+
+size_t ei_sample_scratch_bytes(size_t rows, size_t vocabulary) {
+  (void)rows;
+  (void)vocabulary;
+  return size_t(148) * 16 * (sizeof(float) + sizeof(int));  // partial (value, index) per block and row
+}
+
+ei_status ei_sample_greedy_bf16(const ei_context* ctx, ei_view2 logits, ei_view1 tokens, void* scratch,
+                                size_t scratch_bytes) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_dense(logits);
+    require_dense(tokens);
+    checked_int(logits.shape[1]);
+    if (tokens.shape[0] != logits.shape[0] || !scratch || scratch_bytes < ei_sample_scratch_bytes(0, 0))
+      throw std::invalid_argument("Direct sampling parameters, plan or output capacities are invalid");
+    const int blocks = std::min(148, sample_partial_blocks(logits.shape[1], ctx->multiprocessors));
+    float* best_value = static_cast<float*>(scratch);
+    int* best_index = reinterpret_cast<int*>(best_value + 148 * 16);
+    for_row_groups(logits.shape[0], [&](size_t first, size_t rows) {
+      launch_argmax_partials(static_cast<const bf16*>(logits.data) + first * logits.stride[0], rows, logits.shape[1],
+                             logits.stride[0], best_value, best_index, blocks, stream, false);
+      launch_finalize(best_value, best_index, blocks, int(rows), static_cast<uint32_t*>(tokens.data) + first, nullptr,
+                      nullptr, nullptr, nullptr, nullptr, stream, false);
+    });
+  });
+}
+
+ei_status ei_verify_accept(const ei_context* ctx, const uint32_t* inputs, const uint32_t* targets, size_t rows,
+                           int32_t* context_length, uint32_t* pending, ei_verify_result* result) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    if (!inputs || !targets || !rows || rows > 16 || !context_length || !pending || !result)
+      throw std::invalid_argument("Verify acceptance requires 1..16 rows and non-null device pointers");
+    launch_accept(inputs, targets, int(rows), context_length, pending, result, stream);
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,294 @@
+// Causal verify attention for q_len = k + 1 <= 16 query rows over a session's KV cache
+// (head_dim 128, grouped-query heads).
+//
+// The path is bound by KV bytes, so each KV byte is fetched once: a block owns one KV head and
+// one chunk of the sequence, and serves every query row of every query head of that KV group
+// (rows * heads/kv_heads <= 112 stacked rows, one 16-row MMA tile per warp). K and V tiles of
+// 64 tokens go through shared memory with 16-byte asynchronous copies, double buffered, in a
+// swizzled layout that makes the fragment loads conflict-free. Scores, running maxima and sums
+// stay in FP32; numerators are rounded to BF16 only as the A operand of the PV product while the
+// denominator adds the unrounded values - the staging of the reference kernel
+// (operators/src/cuda/kernels/flash_attn_prefill.cu:236-252). Chunks write (o, m, l) partials to
+// caller scratch and a second kernel merges the live chunks in FP32 and rounds once.
+// The position of the first query row is read from device memory, so a captured graph can be
+// replayed while the context grows; blocks beyond the live length return immediately.
+#include "kernels.cuh"
+
+#include <cfloat>
+
+namespace ei {
+namespace {
+
+constexpr int kTile = 64;          // tokens per shared-memory tile
+constexpr int kDim = 128;
+constexpr int kPartial = 132;      // floats per (split, row, head): 128 outputs, m, l, padding
+constexpr int kTileBytes = kTile * kDim * 2;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const int bytes = valid ? 16 : 0;  // 0 source bytes zero-fills the destination
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending));
+}
+
+// Byte offset of (token, 16-byte chunk) inside a tile: chunk index XOR (token & 7).
+__device__ __forceinline__ int tile_offset(int token, int chunk) {
+  return token * (kDim * 2) + ((chunk ^ (token & 7)) << 4);
+}
+
+__device__ __forceinline__ void load_tile(unsigned char* k_smem, unsigned char* v_smem, const bf16* k,
+                                          const bf16* v, int kv_stride, int first_token, int end_token) {
+  for (int i = threadIdx.x; i < kTile * 16; i += blockDim.x) {
+    const int token = i >> 4, chunk = i & 15;
+    const int absolute = first_token + token;
+    const bool valid = absolute < end_token;
+    const size_t src = size_t(valid ? absolute : first_token) * kv_stride + chunk * 8;
+    cp_async_16(k_smem + tile_offset(token, chunk), k + src, valid);
+    cp_async_16(v_smem + tile_offset(token, chunk), v + src, valid);
+  }
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                                  const void* smem_ptr) {
+  const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(address));
+}
+
+__global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  grid_dependency_wait();
+  const int offset = p.device_offset ? *p.device_offset : p.host_offset;
+  const int length = offset + p.rows;
+  const int split = blockIdx.x, kv_head = blockIdx.y;
+  const int start = split * p.chunk;
+  if (offset < 0 || length > p.capacity || start >= length) return;
+  const int end = min(start + p.chunk, length);
+  const int group = p.heads / p.kv_heads;
+  const int stacked = p.rows * group;  // query rows served by this block
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+
+  unsigned char* k_smem[2] = {smem, smem + 2 * kTileBytes};
+  unsigned char* v_smem[2] = {smem + kTileBytes, smem + 3 * kTileBytes};
+  const bf16* k_base = p.k + size_t(kv_head) * kDim;
+  const bf16* v_base = p.v + size_t(kv_head) * kDim;
+
+  load_tile(k_smem[0], v_smem[0], k_base, v_base, p.kv_stride, start, end);
+  cp_async_commit();
+
+  // Stacked row i = r * group + hq  ->  query row r, query head kv_head * group + hq.
+  const int i_lo = warp * 16 + g, i_hi = i_lo + 8;
+  const bool live_lo = i_lo < stacked, live_hi = i_hi < stacked;
+  const int r_lo = live_lo ? i_lo / group : 0, r_hi = live_hi ? i_hi / group : 0;
+  const int h_lo = kv_head * group + (live_lo ? i_lo % group : 0);
+  const int h_hi = kv_head * group + (live_hi ? i_hi % group : 0);
+  uint32_t qa[8][4];
+  {
+    const bf16* q_lo = p.q + size_t(r_lo) * p.q_stride + size_t(h_lo) * kDim;
+    const bf16* q_hi = p.q + size_t(r_hi) * p.q_stride + size_t(h_hi) * kDim;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qa[kk][0] = live_lo ? *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 2 * c) : 0u;
+      qa[kk][1] = live_hi ? *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 2 * c) : 0u;
+      qa[kk][2] = live_lo ? *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 8 + 2 * c) : 0u;
+      qa[kk][3] = live_hi ? *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 8 + 2 * c) : 0u;
+    }
+  }
+  // Last visible token of each row (causal): offset + r.
+  const int limit_lo = offset + r_lo, limit_hi = offset + r_hi;
+  const float scale = rsqrtf(float(kDim));
+
+  float o[16][4];
+#pragma unroll
+  for (int d = 0; d < 16; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+
+  const int tiles = (end - start + kTile - 1) / kTile;
+  for (int tile = 0; tile < tiles; ++tile) {
+    const int buffer = tile & 1;
+    if (tile + 1 < tiles) {
+      load_tile(k_smem[buffer ^ 1], v_smem[buffer ^ 1], k_base, v_base, p.kv_stride, start + (tile + 1) * kTile,
+                end);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const unsigned char* ks = k_smem[buffer];
+    const unsigned char* vs = v_smem[buffer];
+    const int first = start + tile * kTile;
+
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+      const int token = j * 8 + g;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(ks + tile_offset(token, 2 * kk) + 4 * c);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(ks + tile_offset(token, 2 * kk + 1) + 4 * c);
+        mma_bf16_16816(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+      }
+    }
+    // Scale, mask (causal and beyond-the-end), running maximum.
+    float tile_max_lo = -INFINITY, tile_max_hi = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int t0 = first + j * 8 + 2 * c, t1 = t0 + 1;
+      s[j][0] = t0 <= limit_lo ? s[j][0] * scale : -INFINITY;
+      s[j][1] = t1 <= limit_lo ? s[j][1] * scale : -INFINITY;
+      s[j][2] = t0 <= limit_hi ? s[j][2] * scale : -INFINITY;
+      s[j][3] = t1 <= limit_hi ? s[j][3] * scale : -INFINITY;
+      tile_max_lo = fmaxf(tile_max_lo, fmaxf(s[j][0], s[j][1]));
+      tile_max_hi = fmaxf(tile_max_hi, fmaxf(s[j][2], s[j][3]));
+    }
+    tile_max_lo = fmaxf(tile_max_lo, __shfl_xor_sync(0xffffffffu, tile_max_lo, 1));
+    tile_max_lo = fmaxf(tile_max_lo, __shfl_xor_sync(0xffffffffu, tile_max_lo, 2));
+    tile_max_hi = fmaxf(tile_max_hi, __shfl_xor_sync(0xffffffffu, tile_max_hi, 1));
+    tile_max_hi = fmaxf(tile_max_hi, __shfl_xor_sync(0xffffffffu, tile_max_hi, 2));
+    const float new_lo = fmaxf(m_lo, tile_max_lo), new_hi = fmaxf(m_hi, tile_max_hi);
+    // A row with nothing visible yet keeps m = -inf; use 0 as the exponent base so exp() gives 0.
+    const float base_lo = new_lo == -INFINITY ? 0.0f : new_lo;
+    const float base_hi = new_hi == -INFINITY ? 0.0f : new_hi;
+    const float rescale_lo = __expf(m_lo - base_lo), rescale_hi = __expf(m_hi - base_hi);
+    m_lo = new_lo;
+    m_hi = new_hi;
+    float sum_lo = 0.0f, sum_hi = 0.0f;
+    uint32_t pa[8][2];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p0 = __expf(s[j][0] - base_lo), p1 = __expf(s[j][1] - base_lo);
+      const float p2 = __expf(s[j][2] - base_hi), p3 = __expf(s[j][3] - base_hi);
+      sum_lo += p0 + p1;
+      sum_hi += p2 + p3;
+      pa[j][0] = pack_bf16(p0, p1);
+      pa[j][1] = pack_bf16(p2, p3);
+    }
+    l_lo = l_lo * rescale_lo + sum_lo;  // per-lane partial; the quad is summed at the end
+    l_hi = l_hi * rescale_hi + sum_hi;
+#pragma unroll
+    for (int d = 0; d < 16; ++d) {
+      o[d][0] *= rescale_lo;
+      o[d][1] *= rescale_lo;
+      o[d][2] *= rescale_hi;
+      o[d][3] *= rescale_hi;
+    }
+    // O += P V : k-step t covers tokens 16t..16t+15, n-tile d covers dims 8d..8d+7.
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+#pragma unroll
+      for (int d = 0; d < 16; d += 2) {
+        const int matrix = lane >> 3, row = lane & 7;
+        const int token = t * 16 + (matrix & 1) * 8 + row;
+        const int chunk = d + (matrix >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vs + tile_offset(token, chunk));
+        mma_bf16_16816(o[d], pa[2 * t][0], pa[2 * t][1], pa[2 * t + 1][0], pa[2 * t + 1][1], b0, b1);
+        mma_bf16_16816(o[d + 1], pa[2 * t][0], pa[2 * t][1], pa[2 * t + 1][0], pa[2 * t + 1][1], b2, b3);
+      }
+    }
+    __syncthreads();  // the buffer is refilled two iterations from now
+  }
+  grid_launch_dependents();
+
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  const size_t slots = size_t(p.rows) * p.heads;
+  if (live_lo) {
+    float* dst = p.scratch + (size_t(split) * slots + size_t(r_lo) * p.heads + h_lo) * kPartial;
+#pragma unroll
+    for (int d = 0; d < 16; ++d) *reinterpret_cast<float2*>(dst + d * 8 + 2 * c) = make_float2(o[d][0], o[d][1]);
+    if (c == 0) {
+      dst[128] = m_lo;
+      dst[129] = l_lo;
+    }
+  }
+  if (live_hi) {
+    float* dst = p.scratch + (size_t(split) * slots + size_t(r_hi) * p.heads + h_hi) * kPartial;
+#pragma unroll
+    for (int d = 0; d < 16; ++d) *reinterpret_cast<float2*>(dst + d * 8 + 2 * c) = make_float2(o[d][2], o[d][3]);
+    if (c == 0) {
+      dst[128] = m_hi;
+      dst[129] = l_hi;
+    }
+  }
+}
+
+// One warp per (row, head): merges the live splits in split order.
+__global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionParams p) {
+  grid_dependency_wait();
+  const int slot = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int slots = p.rows * p.heads;
+  if (slot >= slots) return;
+  const int offset = p.device_offset ? *p.device_offset : p.host_offset;
+  const int length = offset + p.rows;
+  if (offset < 0 || length > p.capacity) return;
+  const int splits = (length + p.chunk - 1) / p.chunk;
+  float maximum = -INFINITY;
+  for (int s = 0; s < splits; ++s) maximum = fmaxf(maximum, p.scratch[(size_t(s) * slots + slot) * kPartial + 128]);
+  float denominator = 0.0f;
+  float4 accumulator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int s = 0; s < splits; ++s) {
+    const float* src = p.scratch + (size_t(s) * slots + slot) * kPartial;
+    const float m = src[128];
+    if (m == -INFINITY) continue;  // nothing visible to this row in that split
+    const float weight = __expf(m - maximum);
+    denominator += src[129] * weight;
+    const float4 value = *reinterpret_cast<const float4*>(src + 4 * lane);
+    accumulator.x += value.x * weight;
+    accumulator.y += value.y * weight;
+    accumulator.z += value.z * weight;
+    accumulator.w += value.w * weight;
+  }
+  grid_launch_dependents();
+  const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
+  const int row = slot / p.heads, head = slot - row * p.heads;
+  bf16* dst = p.out + size_t(row) * p.out_stride + size_t(head) * kDim + 4 * lane;
+  uint2 packed;
+  packed.x = pack_bf16(accumulator.x * inverse, accumulator.y * inverse);
+  packed.y = pack_bf16(accumulator.z * inverse, accumulator.w * inverse);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+}  // namespace
+
+int attention_chunk_for(size_t kv_length) {
+  // At most 64 splits; chunks are whole tiles.
+  const size_t tiles = (kv_length + kTile - 1) / kTile;
+  const size_t tiles_per_chunk = std::max<size_t>(1, (tiles + 63) / 64);
+  return int(tiles_per_chunk * kTile);
+}
+
+size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length) {
+  const size_t chunk = attention_chunk_for(kv_length);
+  const size_t splits = (kv_length + chunk - 1) / chunk;
+  return splits * rows * heads * kPartial * sizeof(float);
+}
+
+void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+  const int group = p.heads / p.kv_heads;
+  const int warps = (p.rows * group + 15) / 16;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  EI_CUDA(cudaGetDevice(&device));
+  if (configured_device != device) {
+    EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 4 * kTileBytes));
+    configured_device = device;
+  }
+  launch(verify_attention_kernel, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
+         stream, pdl, p);
+  launch(attention_merge_kernel, dim3((p.rows * p.heads + 3) / 4), dim3(128), 0, stream, pdl, p);
+}
+
+}  // namespace ei

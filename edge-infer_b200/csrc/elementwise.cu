@@ -1,0 +1,292 @@
+// Normalisation, rotary embedding, residual and KV-append kernels of the verify step.
+//
+// BF16 rounding contracts follow the reference CUDA operators so that the staged values
+// agree: RMSNorm rounds x * inv_rms to BF16 and then the weighted product
+// (operators/src/cuda/rms_norm_cuda.cu:87-95); RoPE rounds the table's sine and cosine, each of
+// the four products and both sums (operators/src/cuda/execution.cu:104-117); the residual
+// add is one rounded FP32 sum of two BF16 values (operators/src/cuda/add_cuda.cu:42-62).
+#include "kernels.cuh"
+#include "smallm_gemm.cuh"
+
+namespace ei {
+namespace {
+
+constexpr int kNormThreads = 512;
+constexpr int kNormMaxPerThread = 20;  // 10240 / 512, the reference's width limit
+
+__device__ __forceinline__ float block_sum(float v, float* shared) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) shared[warp] = v;
+  __syncthreads();
+  float total = 0.0f;
+  const int warps = (blockDim.x + 31) >> 5;
+  for (int w = 0; w < warps; ++w) total += shared[w];  // same order in every thread
+  __syncthreads();
+  return total;
+}
+
+__global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const bf16* in, const bf16* weight,
+                                                               bf16* out, int width, float eps) {
+  __shared__ float shared[32];
+  grid_dependency_wait();
+  const bf16* x = in + size_t(blockIdx.x) * width;
+  bf16* y = out + size_t(blockIdx.x) * width;
+  float values[kNormMaxPerThread];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kNormMaxPerThread; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    values[j] = i < width ? __bfloat162float(x[i]) : 0.0f;
+    sum = fmaf(values[j], values[j], sum);
+  }
+  const float total = block_sum(sum, shared);
+  const float inv = rsqrtf(total / float(width) + eps);
+  grid_launch_dependents();
+#pragma unroll
+  for (int j = 0; j < kNormMaxPerThread; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < width) y[i] = __float2bfloat16_rn(round_bf16(values[j] * inv) * __bfloat162float(weight[i]));
+  }
+}
+
+__global__ void add_kernel(const bf16* a, const bf16* b, bf16* out, size_t count) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16_rn(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+}
+
+__global__ void silu_multiply_kernel(const bf16* gate, const bf16* up, bf16* out, size_t count) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16_rn(silu_multiply_value(__bfloat162float(gate[i]), __bfloat162float(up[i])));
+}
+
+__global__ void gather_kernel(const uint32_t* ids, const bf16* table, bf16* out, size_t count, size_t width,
+                              size_t vocabulary) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x) {
+    const uint32_t token = ids[i / width];
+    out[i] = token < vocabulary ? table[size_t(token) * width + i % width] : __float2bfloat16_rn(0.0f);
+  }
+}
+
+__device__ __forceinline__ void rotate_pair(float x, float y, float sine, float cosine, float& first,
+                                            float& second) {
+  sine = round_bf16(sine);
+  cosine = round_bf16(cosine);
+  first = round_bf16(round_bf16(x * cosine) - round_bf16(y * sine));
+  second = round_bf16(round_bf16(x * sine) + round_bf16(y * cosine));
+}
+
+__global__ void rope_kernel(bf16* data, size_t row_stride, size_t head_dim, const float* table,
+                            size_t table_stride, size_t offset, const size_t* offsets, const int* pingpong) {
+  const size_t pair = threadIdx.x, half = head_dim / 2;
+  if (pair >= half) return;
+  const size_t position = blockIdx.x + (offsets ? offsets[pingpong ? *pingpong : 0] : offset);
+  bf16* head = data + size_t(blockIdx.x) * row_stride + size_t(blockIdx.y) * head_dim;
+  float first, second;
+  rotate_pair(__bfloat162float(head[pair]), __bfloat162float(head[pair + half]),
+              table[position * table_stride + 2 * pair], table[position * table_stride + 2 * pair + 1], first,
+              second);
+  head[pair] = __float2bfloat16_rn(first);
+  head[pair + half] = __float2bfloat16_rn(second);
+}
+
+__global__ void store_kv_kernel(const bf16* source, bf16* cache, size_t count, size_t rows, size_t width,
+                                size_t capacity, size_t offset, const size_t* device_offset) {
+  const size_t start_row = device_offset ? *device_offset : offset;
+  if (start_row > capacity || rows > capacity - start_row) return;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
+    cache[start_row * width + i] = source[i];
+}
+
+__global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedParams p) {
+  __shared__ float shared[32];
+  __shared__ uint32_t token_shared;
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  if (threadIdx.x == 0) {
+    uint32_t token;
+    if (p.tokens) {
+      token = p.tokens[row];
+    } else if (row == 0) {
+      token = p.control->pending;
+    } else {
+      const DraftSource source = *p.source;
+      const long long index = (long long)p.control->context + row - source.base;
+      token = (source.drafts && index >= 0 && index < source.count) ? source.drafts[index] : 0u;
+    }
+    p.step_tokens[row] = token;
+    if (token >= uint32_t(p.vocab)) atomicOr(&p.control->status, 2);
+    if (row == 0 && p.control->context + p.rows > p.capacity) atomicOr(&p.control->status, 1);
+    token_shared = token;
+  }
+  __syncthreads();
+  const uint32_t token = token_shared;
+  const bf16* source = p.table + size_t(token < uint32_t(p.vocab) ? token : 0) * p.hidden;
+  bf16* residual = p.residual + size_t(row) * p.hidden;
+  bf16* normed = p.normed + size_t(row) * p.hidden;
+  float values[kNormMaxPerThread];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kNormMaxPerThread; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    float value = 0.0f;
+    if (i < p.hidden) {
+      const bf16 raw = token < uint32_t(p.vocab) ? source[i] : __float2bfloat16_rn(0.0f);
+      residual[i] = raw;
+      value = __bfloat162float(raw);
+    }
+    values[j] = value;
+    sum = fmaf(value, value, sum);
+  }
+  const float total = block_sum(sum, shared);
+  const float inv = rsqrtf(total / float(p.hidden) + p.eps);
+  grid_launch_dependents();
+#pragma unroll
+  for (int j = 0; j < kNormMaxPerThread; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < p.hidden)
+      normed[i] = __float2bfloat16_rn(round_bf16(values[j] * inv) * __bfloat162float(p.norm_weight[i]));
+  }
+}
+
+// One warp per (row, head); lane l owns rotation pairs 2l and 2l+1, i.e. elements
+// {2l, 2l+1} of the first half and {64+2l, 64+2l+1} of the second.
+__global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams p) {
+  grid_dependency_wait();
+  const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int per_row = p.heads + 2 * p.kv_heads;
+  if (warp_global >= p.rows * per_row) return;
+  const int row = warp_global / per_row, slot = warp_global - row * per_row;
+  const int context = p.control->context;
+  const int position = context + row;
+  if (context + p.rows > p.capacity || position >= p.max_positions) return;  // status set by the embed kernel
+  bf16* head = p.qkv + size_t(row) * p.qkv_stride + size_t(slot) * 128;
+  if (slot >= p.heads + p.kv_heads) {  // value head: append as is
+    const int kvh = slot - p.heads - p.kv_heads;
+    const uint2 v = *reinterpret_cast<const uint2*>(head + lane * 4);
+    *reinterpret_cast<uint2*>(p.v_cache + (size_t(position) * p.kv_heads + kvh) * 128 + lane * 4) = v;
+    return;
+  }
+  const bool is_query = slot < p.heads;
+  const uint32_t lo = *reinterpret_cast<const uint32_t*>(head + 2 * lane);
+  const uint32_t hi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
+  float x0 = bf16_lo(lo), x1 = bf16_hi(lo), y0 = bf16_lo(hi), y1 = bf16_hi(hi);
+  const bf16* norm = is_query ? p.q_norm : p.k_norm;
+  if (norm) {
+    float sum = fmaf(x0, x0, fmaf(x1, x1, fmaf(y0, y0, y1 * y1)));
+    sum = warp_sum(sum);
+    const float inv = rsqrtf(sum / 128.0f + p.eps);
+    const uint32_t wl = *reinterpret_cast<const uint32_t*>(norm + 2 * lane);
+    const uint32_t wh = *reinterpret_cast<const uint32_t*>(norm + 64 + 2 * lane);
+    x0 = round_bf16(round_bf16(x0 * inv) * bf16_lo(wl));
+    x1 = round_bf16(round_bf16(x1 * inv) * bf16_hi(wl));
+    y0 = round_bf16(round_bf16(y0 * inv) * bf16_lo(wh));
+    y1 = round_bf16(round_bf16(y1 * inv) * bf16_hi(wh));
+  }
+  const float4 trig = *reinterpret_cast<const float4*>(p.rope_table + size_t(position) * 128 + 4 * lane);
+  float a0, b0, a1, b1;
+  rotate_pair(x0, y0, trig.x, trig.y, a0, b0);
+  rotate_pair(x1, y1, trig.z, trig.w, a1, b1);
+  const uint32_t out_lo = pack_bf16(a0, a1), out_hi = pack_bf16(b0, b1);
+  if (is_query) {
+    *reinterpret_cast<uint32_t*>(head + 2 * lane) = out_lo;
+    *reinterpret_cast<uint32_t*>(head + 64 + 2 * lane) = out_hi;
+  } else {
+    bf16* dst = p.k_cache + (size_t(position) * p.kv_heads + (slot - p.heads)) * 128;
+    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = out_lo;
+    *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = out_hi;
+  }
+}
+
+__global__ void __launch_bounds__(kNormThreads) residual_norm_kernel(const ResidualNormParams p) {
+  __shared__ float shared[32];
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  bf16* residual = p.residual + size_t(row) * p.hidden;
+  bf16* normed = p.normed + size_t(row) * p.hidden;
+  float values[kNormMaxPerThread];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kNormMaxPerThread; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    float value = 0.0f;
+    if (i < p.hidden) {
+      float projection = 0.0f;
+      for (int s = 0; s < p.ksplit; ++s) projection += p.partial[(size_t(s) * p.rows + row) * p.hidden + i];
+      if (p.bias) projection += __bfloat162float(p.bias[i]);
+      value = round_bf16(__bfloat162float(residual[i]) + round_bf16(projection));
+      residual[i] = __float2bfloat16_rn(value);
+    }
+    values[j] = value;
+    sum = fmaf(value, value, sum);
+  }
+  const float total = block_sum(sum, shared);
+  const float inv = rsqrtf(total / float(p.hidden) + p.eps);
+  grid_launch_dependents();
+#pragma unroll
+  for (int j = 0; j < kNormMaxPerThread; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < p.hidden)
+      normed[i] = __float2bfloat16_rn(round_bf16(values[j] * inv) * __bfloat162float(p.norm_weight[i]));
+  }
+}
+
+int blocks_for(size_t count, int multiprocessors) {
+  return int(std::max<size_t>(1, std::min<size_t>((count + 255) / 256, size_t(multiprocessors) * 32)));
+}
+
+}  // namespace
+
+void launch_rms_norm(const bf16* in, const bf16* weight, bf16* out, size_t rows, size_t width, float eps,
+                     cudaStream_t stream, bool pdl) {
+  launch(rms_norm_kernel, dim3(unsigned(rows)), dim3(kNormThreads), 0, stream, pdl, in, weight, out,
+         int(width), eps);
+}
+
+void launch_add(const bf16* a, const bf16* b, bf16* out, size_t count, cudaStream_t stream) {
+  add_kernel<<<blocks_for(count, 148), 256, 0, stream>>>(a, b, out, count);
+  check_launch();
+}
+
+void launch_silu_multiply(const bf16* gate, const bf16* up, bf16* out, size_t count, cudaStream_t stream) {
+  silu_multiply_kernel<<<blocks_for(count, 148), 256, 0, stream>>>(gate, up, out, count);
+  check_launch();
+}
+
+void launch_gather(const uint32_t* ids, const bf16* table, bf16* out, size_t rows, size_t width,
+                   size_t vocabulary, int multiprocessors, cudaStream_t stream) {
+  gather_kernel<<<blocks_for(rows * width, multiprocessors), 256, 0, stream>>>(ids, table, out, rows * width,
+                                                                             width, vocabulary);
+  check_launch();
+}
+
+void launch_rope(bf16* data, size_t rows, size_t heads, size_t head_dim, size_t row_stride, const float* table,
+                 size_t table_stride, size_t offset, const size_t* offsets, const int* pingpong,
+                 cudaStream_t stream) {
+  rope_kernel<<<dim3(unsigned(rows), unsigned(heads)), unsigned(head_dim / 2), 0, stream>>>(
+      data, row_stride, head_dim, table, table_stride, offset, offsets, pingpong);
+  check_launch();
+}
+
+void launch_store_kv(const bf16* source, bf16* cache, size_t rows, size_t width, size_t capacity, size_t offset,
+                     const size_t* device_offset, int multiprocessors, cudaStream_t stream) {
+  store_kv_kernel<<<blocks_for(rows * width, multiprocessors), 256, 0, stream>>>(
+      source, cache, rows * width, rows, width, capacity, offset, device_offset);
+  check_launch();
+}
+
+void launch_embed_norm(const EmbedParams& p, cudaStream_t stream, bool pdl) {
+  launch(embed_norm_kernel, dim3(p.rows), dim3(kNormThreads), 0, stream, pdl, p);
+}
+
+void launch_qk_norm_rope_store(const QkvParams& p, cudaStream_t stream, bool pdl) {
+  const int warps = p.rows * (p.heads + 2 * p.kv_heads);
+  launch(qk_norm_rope_store_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, pdl, p);
+}
+
+void launch_residual_norm(const ResidualNormParams& p, cudaStream_t stream, bool pdl) {
+  launch(residual_norm_kernel, dim3(p.rows), dim3(kNormThreads), 0, stream, pdl, p);
+}
+
+}  // namespace ei
