@@ -104,6 +104,7 @@ PROTOTYPES = {
     "ei_linear_scratch_bytes": (_Z, [_Z, _Z, _Z]),
     "ei_linear_bf16": (_S, [C.POINTER(Context), View2, C.POINTER(DenseWeight), View2, _P, _Z]),
     "ei_awq_linear_bf16": (_S, [C.POINTER(Context), View2, C.POINTER(AwqWeight), View2, _P, _Z]),
+    "ei_awq_gate_up_silu_bf16": (_S, [C.POINTER(Context), View2, C.POINTER(AwqWeight), View2]),
     "ei_add_bf16": (_S, [C.POINTER(Context), Array, Array, Array]),
     "ei_silu_multiply_bf16": (_S, [C.POINTER(Context), Array, Array, Array]),
     "ei_rms_norm_bf16": (_S, [C.POINTER(Context), Array, Array, Array, _Z, _Z, C.c_float]),

@@ -247,6 +247,38 @@ ei_status ei_awq_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_awq
   });
 }
 
+ei_status ei_awq_gate_up_silu_bf16(const ei_context* ctx, ei_view2 input, const ei_awq_weight* weight,
+                                   ei_view2 output) {
+  return guarded([&] {
+    cudaStream_t stream = stream_of(ctx);
+    require_dense(input);
+    require_dense(output);
+    if (!weight || !weight->qweight || !weight->scales || !weight->zeros || weight->output_features % 2 ||
+        input.shape[1] != size_t(weight->input_features) || output.shape[0] != input.shape[0] ||
+        output.shape[1] != size_t(weight->output_features / 2))
+      throw std::invalid_argument("Fused gate/up projection input/output dimensions are invalid");
+    const int K = weight->input_features, N = weight->output_features, rows = int(input.shape[0]);
+    GemmPlan plan;
+    if (rows <= 16 && weight->group_size == 128 && aligned16(weight->qweight) && aligned16(input.data))
+      plan = plan_gemm(true, rows, N, K, kEpiSiluPair, ctx->multiprocessors, smem_limit_of(ctx), false);
+    if (!plan.fast)
+      throw std::invalid_argument(
+          "Fused gate/up projection needs rows <= 16, group_size 128, K % 256 == 0 and 16-byte aligned operands");
+    GemmParams p{};
+    p.x = static_cast<const bf16*>(input.data); p.x_stride = K; p.M = rows; p.K = K; p.N = N;
+    p.qweight = weight->qweight;
+    p.scales = static_cast<const bf16*>(weight->scales);
+    p.zeros = weight->zeros;
+    p.padded_groups = weight->padded_groups;
+    p.zero_stride = (K / 128 + 7) / 8;
+    p.bias = static_cast<const bf16*>(weight->bias);
+    p.out = static_cast<bf16*>(output.data); p.out_stride = N / 2;
+    p.ksplit = 1;
+    p.epilogue = kEpiSiluPair;
+    launch_gemm(plan, true, p, stream, false);
+  });
+}
+
 ei_status ei_add_bf16(const ei_context* ctx, ei_array a, ei_array b, ei_array out) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);

@@ -56,6 +56,11 @@ def awq_linear(ctx, input, weight: abi.AwqWeight, output, scratch=None) -> None:
     abi.check(_lib().ei_awq_linear_bf16(C.byref(ctx), abi.view2(input), C.byref(weight), abi.view2(output), ptr, size))
 
 
+def awq_gate_up_silu(ctx, input, weight: abi.AwqWeight, output) -> None:
+    """Fused SwiGLU projection over a weight whose rows are [gate; up]: output = silu(gate) * up, staged as BF16."""
+    abi.check(_lib().ei_awq_gate_up_silu_bf16(C.byref(ctx), abi.view2(input), C.byref(weight), abi.view2(output)))
+
+
 def add(ctx, a, b, output) -> None:
     abi.check(_lib().ei_add_bf16(C.byref(ctx), abi.array(a), abi.array(b), abi.array(output)))
 

@@ -98,6 +98,14 @@ ei_status ei_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_dense_w
 ei_status ei_awq_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_awq_weight* weight,
                              ei_view2 output, void* scratch, size_t scratch_bytes);
 
+/* Fused SwiGLU projection, the step's largest kernel: `weight` holds the gate rows followed by the up rows
+ * ([2F, K]; bias, if any, [2F]); out[rows, F] = round(round(silu(round(gate))) * round(up)).
+ * ref: the reference issues two awq_linear calls and silu_multiply (runtime/include/execution/decoder.hpp:162-165,
+ * operators/src/cuda/silu_cuda.cu:45-56); every rounding point of that sequence is kept. rows <= 16,
+ * group_size 128, K % 256 == 0, F % 8 == 0. */
+ei_status ei_awq_gate_up_silu_bf16(const ei_context* ctx, ei_view2 input, const ei_awq_weight* weight,
+                                   ei_view2 output);
+
 /* ---- element-wise / normalisation ------------------------------------------------------------- */
 /* ref: execution.hpp:72-74, add_cuda.cu:144-180 add<T>. */
 ei_status ei_add_bf16(const ei_context* ctx, ei_array a, ei_array b, ei_array out);
@@ -217,8 +225,9 @@ ei_status ei_session_decode(ei_session* session, uint32_t token, const void** lo
 ei_status ei_session_verify(ei_session* session, const uint32_t* host_tokens, size_t rows,
                             ei_verify_result* result, const void** logits);
 /* Asynchronous form for a device-resident loop: row 0 is the pending token kept on the device by the
- * previous step, rows 1..k come from device_drafts[context_length + i - 1 - draft_base] (a device array
- * of the draft token proposed for each absolute position). Enqueues the step and returns without
+ * previous step, row i >= 1 is device_drafts[context_length + i - draft_base]: device_drafts[j] is the
+ * token proposed for absolute position draft_base + j, and row i of a step sits at position
+ * context_length + i. Enqueues the step and returns without
  * synchronising; results accumulate in the session (ei_session_drain). */
 ei_status ei_session_verify_enqueue(ei_session* session, const uint32_t* device_drafts, size_t draft_count,
                                     size_t draft_base, size_t rows);
