@@ -311,12 +311,16 @@ def attention_case(torch, package, oracle, ctx, rows, heads, kv_heads, length, d
         ops.attention_prefill(ctx, dq, dk[:length], dv[:length], out, offset, scratch)
     torch.cuda.synchronize()
     fq, fk, fv = syn.bf16_to_float(q), syn.bf16_to_float(k[:length]), syn.bf16_to_float(v[:length])
-    ref = oracle.op_attention(fq, fk, fv, offset, 0)              # runtime/src/qwen.cpp:382-403 arithmetic
-    got = syn.bf16_to_float(to_host(out))
-    bound = 2.5e-4 + 0.008 * np.maximum(np.abs(got), np.abs(ref))
-    assert np.all(np.abs(got - ref) <= bound), float(np.abs(got - ref).max())
+    exact = oracle.op_attention(fq, fk, fv, offset, 0)            # runtime/src/qwen.cpp:382-403 arithmetic
     staged = oracle.op_attention(fq, fk, fv, offset, 1)           # BF16 numerators, exact accumulation
-    assert np.sqrt(((got - staged) ** 2).mean()) <= 2.0 ** -8 * np.sqrt((staged ** 2).mean()) + 1e-6
+    got = syn.bf16_to_float(to_host(out))
+    # Element-wise against the staged value: both round the numerators to BF16, though relative to different
+    # running maxima, and both round the output once.
+    bound = 2.5e-4 + 0.008 * np.maximum(np.abs(got), np.abs(staged)) + 2.0 ** -7 * np.abs(staged)
+    assert np.all(np.abs(got - staged) <= bound), float(np.abs(got - staged).max())
+    # In the mean the kernel must be as close to the reference executor's FP32 attention as the staged ideal is.
+    rms = lambda a: float(np.sqrt((a ** 2).mean()))               # noqa: E731
+    assert rms(got - exact) <= 1.25 * rms(staged - exact) + 1e-6, (rms(got - exact), rms(staged - exact))
     return got
 
 
