@@ -223,40 +223,59 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   }
 }
 
-// One warp per (row, head): merges the live splits in split order.
+// One block of four warps per (row, head). The live splits (at most 64) are read in parallel: thread s
+// fetches split s's maximum and sum, the block agrees on the global maximum, then warp w accumulates
+// splits w, w+4, ... and the four partial sums are added in warp order. The order of every addition is
+// fixed, so replays give identical bits.
 __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionParams p) {
+  __shared__ float weights[64];
+  __shared__ float warp_values[4];
+  __shared__ float4 partial_out[4][32];
   grid_dependency_wait();
-  const int slot = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+  const int slot = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = p.rows * p.heads;
-  if (slot >= slots) return;
   const int offset = p.device_offset ? *p.device_offset : p.host_offset;
   const int length = offset + p.rows;
   if (offset < 0 || length > p.capacity) return;
-  const int splits = (length + p.chunk - 1) / p.chunk;
-  float maximum = -INFINITY;
-  for (int s = 0; s < splits; ++s) maximum = fmaxf(maximum, p.scratch[(size_t(s) * slots + slot) * kPartial + 128]);
-  float denominator = 0.0f;
-  float4 accumulator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  for (int s = 0; s < splits; ++s) {
-    const float* src = p.scratch + (size_t(s) * slots + slot) * kPartial;
-    const float m = src[128];
-    if (m == -INFINITY) continue;  // nothing visible to this row in that split
-    const float weight = __expf(m - maximum);
-    denominator += src[129] * weight;
-    const float4 value = *reinterpret_cast<const float4*>(src + 4 * lane);
-    accumulator.x += value.x * weight;
-    accumulator.y += value.y * weight;
-    accumulator.z += value.z * weight;
-    accumulator.w += value.w * weight;
+  const int splits = min(64, (length + p.chunk - 1) / p.chunk);
+  float m = -INFINITY, l = 0.0f;
+  if (int(threadIdx.x) < splits) {
+    const float* src = p.scratch + (size_t(threadIdx.x) * slots + slot) * kPartial;
+    m = src[128];
+    l = src[129];
   }
+  float maximum = warp_max(m);
+  if (lane == 0) warp_values[warp] = maximum;
+  __syncthreads();
+  maximum = fmaxf(fmaxf(warp_values[0], warp_values[1]), fmaxf(warp_values[2], warp_values[3]));
+  const float weight = m == -INFINITY ? 0.0f : __expf(m - maximum);  // a split with nothing visible counts 0
+  if (threadIdx.x < 64) weights[threadIdx.x] = weight;
+  float denominator = warp_sum(l * weight);
+  __syncthreads();
+  if (lane == 0) warp_values[warp] = denominator;
+  float4 accumulator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+  for (int s = warp; s < splits; s += 4) {
+    const float4 value = *reinterpret_cast<const float4*>(p.scratch + (size_t(s) * slots + slot) * kPartial + 4 * lane);
+    const float w = weights[s];
+    accumulator.x += value.x * w;
+    accumulator.y += value.y * w;
+    accumulator.z += value.z * w;
+    accumulator.w += value.w * w;
+  }
+  partial_out[warp][lane] = accumulator;
+  __syncthreads();
   grid_launch_dependents();
+  if (warp != 0) return;
+  denominator = (warp_values[0] + warp_values[1]) + (warp_values[2] + warp_values[3]);
+  const float4 a = partial_out[0][lane], b = partial_out[1][lane], c = partial_out[2][lane], d = partial_out[3][lane];
   const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
   const int row = slot / p.heads, head = slot - row * p.heads;
   bf16* dst = p.out + size_t(row) * p.out_stride + size_t(head) * kDim + 4 * lane;
   uint2 packed;
-  packed.x = pack_bf16(accumulator.x * inverse, accumulator.y * inverse);
-  packed.y = pack_bf16(accumulator.z * inverse, accumulator.w * inverse);
+  packed.x = pack_bf16(((a.x + b.x) + (c.x + d.x)) * inverse, ((a.y + b.y) + (c.y + d.y)) * inverse);
+  packed.y = pack_bf16(((a.z + b.z) + (c.z + d.z)) * inverse, ((a.w + b.w) + (c.w + d.w)) * inverse);
   *reinterpret_cast<uint2*>(dst) = packed;
 }
 
@@ -288,7 +307,7 @@ void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool
   }
   launch(verify_attention_kernel, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
          stream, pdl, p);
-  launch(attention_merge_kernel, dim3((p.rows * p.heads + 3) / 4), dim3(128), 0, stream, pdl, p);
+  launch(attention_merge_kernel, dim3(p.rows * p.heads), dim3(128), 0, stream, pdl, p);
 }
 
 }  // namespace ei

@@ -1,5 +1,5 @@
 // Dispatch, planning and fallbacks for the small-M weight-streaming GEMM.
-#include "smallm_gemm.cuh"
+#include "awq_stream.cuh"
 
 #include <algorithm>
 
@@ -56,11 +56,12 @@ __global__ void dense_generic_kernel(const bf16* x, int x_stride, const bf16* w,
 
 namespace {
 
-size_t part_bytes(int tiles_per_item) { return size_t(2) * kGemmWarps * tiles_per_item * 128 * sizeof(float); }
+// Two buffers of per-warp FP32 partials: 16 warps x 136 floats each.
+constexpr size_t kPartBytes = size_t(2) * kGemmWarps * 136 * sizeof(float);
 
-template <bool kAwq, bool kHigh, int kTiles, int kUnits, int kDepth>
+template <bool kAwq, bool kHigh, int kUnits, int kDepth>
 void launch_instance(const GemmPlan& plan, const GemmParams& params, cudaStream_t stream, bool pdl) {
-  auto kernel = smallm_gemm_kernel<kAwq, kHigh, kTiles, kUnits, kDepth>;
+  auto kernel = smallm_gemm_kernel<kAwq, kHigh, kUnits, kDepth>;
   static thread_local int configured_device = -1;
   int device = 0;
   EI_CUDA(cudaGetDevice(&device));
@@ -72,12 +73,13 @@ void launch_instance(const GemmPlan& plan, const GemmParams& params, cudaStream_
   launch(kernel, dim3(plan.grid), dim3(kGemmThreads), plan.smem, stream, pdl, params);
 }
 
-template <bool kAwq, int kTiles, int kUnits, int kDepth>
+// Deeper prefetch where only the low eight rows hold fragments (half the pinned registers).
+template <bool kAwq, int kUnits, int kDepthHigh, int kDepthLow>
 void launch_high(const GemmPlan& plan, const GemmParams& params, cudaStream_t stream, bool pdl) {
   if (plan.high)
-    launch_instance<kAwq, true, kTiles, kUnits, kDepth>(plan, params, stream, pdl);
+    launch_instance<kAwq, true, kUnits, kDepthHigh>(plan, params, stream, pdl);
   else
-    launch_instance<kAwq, false, kTiles, kUnits, kDepth>(plan, params, stream, pdl);
+    launch_instance<kAwq, false, kUnits, kDepthLow>(plan, params, stream, pdl);
 }
 
 }  // namespace
@@ -90,47 +92,52 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
   const bool pair = epilogue == kEpiSiluPair;
   if (pair && N % 16) return plan;
   plan.high = M > 8;
-  const int max_units = awq ? 2 : (pair ? 2 : 4);
-  const int tiles = N / 8;
-  static const int candidates[] = {1, 2, 3, 4, 6, 8, 12, 16};
-  for (int ks : candidates) {
-    if (K % (ks * unit_k)) continue;
-    const int kslice = K / ks;
-    const int units = kslice / unit_k;
-    const int per_warp = (units + kGemmWarps - 1) / kGemmWarps;
-    if (per_warp > max_units) continue;
-    int tiles_per_item = pair ? 2 : (awq ? (per_warp == 1 ? 2 : 1) : 1);
-    // A second tile per item only pays when every block still gets several items.
-    if (!pair && tiles_per_item == 2 && tiles / 2 < 4 * multiprocessors / ks) tiles_per_item = 1;
-    const size_t smem = size_t(kslice) * 16 * (plan.high ? 2 : 1) + part_bytes(tiles_per_item);
-    if (smem > smem_limit) continue;
-    if (ks > 1 && (!allow_split || (epilogue != kEpiStore && epilogue != kEpiPartial))) return plan;
-    plan.fast = true;
-    plan.ksplit = ks;
-    plan.units_per_warp = per_warp == 3 ? 4 : per_warp;
-    plan.tiles_per_item = tiles_per_item;
-    plan.smem = smem;
-    const int items = pair ? tiles / 2 : (tiles + tiles_per_item - 1) / tiles_per_item;
-    const int groups = std::max(1, std::min(multiprocessors / ks, items));
-    plan.grid = groups * ks;
-    return plan;
+  // Units one warp may own: int4 pins its fragments in registers (one unit); BF16 reads them from shared memory.
+  const int max_units = awq ? 1 : 4;
+  const int units_total = K / unit_k;
+  const int ks = (units_total + kGemmWarps * max_units - 1) / (kGemmWarps * max_units);
+  if (ks > 1 && (!allow_split || (epilogue != kEpiStore && epilogue != kEpiPartial))) return plan;
+  if (ks > 16) return plan;
+  const int units = (units_total + ks - 1) / ks;  // the largest slice
+  int per_warp = (units + kGemmWarps - 1) / kGemmWarps;
+  if (per_warp == 3) per_warp = 4;
+  const int chunks = pair ? N / 16 : N / 8;
+  const int groups = std::max(1, std::min(multiprocessors / ks, chunks));
+  size_t smem = kPartBytes + size_t(units) * unit_k * 16 * (plan.high ? 2 : 1);
+  if (awq) {
+    if (epilogue == kEpiArgmax) return plan;  // the vocabulary head is a dense matrix
+    plan.tiles_per_block = ((chunks + groups - 1) / groups) * (pair ? 2 : 1);
+    smem = awq_stream_layout(units, plan.tiles_per_block).total;
   }
+  if (smem > smem_limit) return plan;
+  plan.fast = true;
+  plan.ksplit = ks;
+  plan.units_per_warp = per_warp;
+  plan.smem = smem;
+  plan.grid = groups * ks;
   return plan;
 }
 
 void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
-  const int T = plan.tiles_per_item, U = plan.units_per_warp;
+  const int U = plan.units_per_warp;
   if (awq) {
-    if (T == 2 && U == 1) return launch_high<true, 2, 1, 3>(plan, p, stream, pdl);
-    if (T == 1 && U == 1) return launch_high<true, 1, 1, 4>(plan, p, stream, pdl);
-    if (T == 1 && U == 2) return launch_high<true, 1, 2, 2>(plan, p, stream, pdl);
-    if (T == 2 && U == 2) return launch_high<true, 2, 2, 2>(plan, p, stream, pdl);
+    static thread_local int configured_device = -1;
+    int device = 0;
+    EI_CUDA(cudaGetDevice(&device));
+    if (configured_device != device) {
+      EI_CUDA(cudaFuncSetAttribute(awq_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      EI_CUDA(cudaFuncSetAttribute(awq_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      configured_device = device;
+    }
+    if (plan.high)
+      launch(awq_stream_kernel<true>, dim3(plan.grid), dim3(kGemmThreads), plan.smem, stream, pdl, p, plan.tiles_per_block);
+    else
+      launch(awq_stream_kernel<false>, dim3(plan.grid), dim3(kGemmThreads), plan.smem, stream, pdl, p, plan.tiles_per_block);
+    return;
   } else {
-    if (T == 1 && U == 1) return launch_high<false, 1, 1, 4>(plan, p, stream, pdl);
-    if (T == 1 && U == 2) return launch_high<false, 1, 2, 3>(plan, p, stream, pdl);
-    if (T == 1 && U == 4) return launch_high<false, 1, 4, 2>(plan, p, stream, pdl);
-    if (T == 2 && U == 1) return launch_high<false, 2, 1, 3>(plan, p, stream, pdl);
-    if (T == 2 && U == 2) return launch_high<false, 2, 2, 2>(plan, p, stream, pdl);
+    if (U == 1) return launch_high<false, 1, 6, 6>(plan, p, stream, pdl);
+    if (U == 2) return launch_high<false, 2, 4, 4>(plan, p, stream, pdl);
+    if (U == 4) return launch_high<false, 4, 2, 2>(plan, p, stream, pdl);
   }
   throw std::invalid_argument("small-M GEMM plan has no kernel instance");
 }

@@ -1,26 +1,29 @@
 // Small-M (<= 16 rows) weight-streaming GEMM for sm_100a: out[M,N] = x[M,K] * W[N,K]^T (+ bias).
 //
-// The path is HBM-bound: every weight byte is read exactly once per call, straight from
-// global memory into registers with 128-bit loads (each quad of lanes reads 128 contiguous
-// bytes of one weight row), dequantised in registers and fed to mma.sync.m16n8k16 as the B
-// operand. The <= 16 activation rows are staged once per block in shared memory in the exact
-// order the A fragments need, so a fragment is one conflict-free 128-bit shared load.
-// Weights never pass through shared memory, which is why the register-operand MMA is used
-// rather than a shared-memory-operand tensor-core path: with 16 rows the tensor pipe is
-// nearly idle either way and the instruction budget goes to the int4 -> BF16 conversion.
+// The path is HBM-bound on bytes and, for int4 weights, issue-bound on the nibble -> BF16 conversion, so
+// the inner loop is stripped to that conversion and the MMA:
+//  * every weight byte is read exactly once, straight from global memory into registers with 128-bit
+//    loads that bypass L1 (each quad of lanes reads 128 contiguous bytes of one weight row); the loads of
+//    the next kDepth items are kept in flight in registers while the current item is computed, and nothing
+//    is computed from a loaded word before its item is consumed (a dependent instruction would stall the
+//    in-order issue of the loads behind it);
+//  * the activations never change while a block runs and each of its 16 warps always works on the same
+//    slice of the input features (K is dealt to the warps in units of 256 inputs for int4, 64 for BF16), so
+//    a warp loads its A fragments once, already in the register order mma.sync wants, and keeps them in
+//    registers for the whole kernel: the loop has no shared-memory loads and no register shuffles;
+//  * weights are dequantised in registers and fed to mma.sync.m16n8k16 as the B operand. A shared-memory
+//    operand tensor-core path (tcgen05) would need the dequantised tile written to shared memory first;
+//    with <= 16 rows the tensor pipe is idle either way and the cost that matters is the conversion.
 //
-// Work decomposition: persistent blocks of 16 warps. A "tile" is 8 output features; an item
-// is kTiles tiles processed together (they share the A fragments). Within an item the K range
-// is cut into units (256 inputs for int4, 64 for BF16) dealt round-robin to the 16 warps;
-// warps write FP32 partial accumulators to shared memory and 128 * kTiles threads add them in
-// warp order, so results do not depend on scheduling. Loads for the next kDepth items are
-// kept in flight in registers while the current one is computed. An optional split of K over
-// blocks writes FP32 partials to caller scratch for a separate fixed-order reduction.
+// Work decomposition: persistent blocks of 16 warps. An item is one tile of 8 output features. Per item the
+// warps write their FP32 partial accumulators to shared memory and all 512 threads add them in a fixed order
+// (4 partials per thread, parts combined by shuffles), so results do not depend on scheduling. Input features beyond 16 units per block are split over blocks (ksplit) that
+// write FP32 partials to caller scratch for a separate fixed-order reduction.
 //
-// Rounding contract (reference operators/src/cuda/kernels/awq_gemv_gemm.cu:119-127, 318-329):
-// int4 weights are dequantised as round_bf16((w - z) * scale) - here computed as an exact BF16
-// subtraction followed by one correctly rounded BF16 multiply, which gives the same bits -
-// products accumulate in FP32, the bias joins the FP32 sum and the result is rounded once.
+// Rounding contract (reference operators/src/cuda/kernels/awq_gemv_gemm.cu:119-127, 318-329): int4 weights
+// are dequantised as round_bf16((w - z) * scale) - computed as an exact BF16 subtraction followed by one
+// correctly rounded BF16 multiply, which gives the same bits - products accumulate in FP32, the bias joins
+// the FP32 sum and the result is rounded once.
 #pragma once
 
 #include "common.cuh"
@@ -52,13 +55,15 @@ struct GemmParams {
   float* partial;         // [ksplit, M, N]
   float* best_value;      // kEpiArgmax: [grid, 16]
   int* best_index;        //             [grid, 16]
+  int* status;            // optional device word; bit 2 is set if a bounded wait on a bulk copy gave up
 };
 
 constexpr int kGemmWarps = 16;
 constexpr int kGemmThreads = kGemmWarps * 32;
 
 __device__ __forceinline__ float silu_value(float x) {
-  // Same branches as the reference operator (operators/src/cuda/silu_cuda.cu:11-32).
+  // Same branches as the reference operator (operators/src/cuda/silu_cuda.cu:11-32), whose build uses
+  // fast-math for the exponential and the division of the main branch.
   if ((__float_as_uint(x) & 0x7fffffffu) <= 0x01000000u) {
     const float zero = __uint_as_float(__float_as_uint(x) & 0x80000000u);
     return __fmaf_ieee_rn(x, 0.5f, zero);
@@ -70,7 +75,7 @@ __device__ __forceinline__ float silu_value(float x) {
     asm("cvt.rn.f32.f64 %0, %1;" : "=f"(r) : "d"(a));
     return r;
   }
-  return x / (1.0f + expf(-x));
+  return __fdividef(x, 1.0f + __expf(-x));
 }
 
 __device__ __forceinline__ float silu_multiply_value(float gate, float up) {
@@ -79,111 +84,156 @@ __device__ __forceinline__ float silu_multiply_value(float gate, float up) {
   return round_bf16(__fmaf_ieee_rn(activated, up, zero));
 }
 
-// Shared-memory image of the activations: 16-byte cells of 8 consecutive inputs of one row.
-// Cell (row r < 8, kb) lives at ((kb * 8 + (r ^ swizzle(kb))) * 16; rows 8..15 in a second
-// array of the same shape. kShift picks the kb bits that differ between the four lanes of a
-// quad so that a quarter-warp's 128-bit loads fall into eight distinct bank groups.
-template <int kShift>
-__device__ __forceinline__ int x_cell(int kb, int r) {
-  return (kb * 8 + (r ^ (((kb >> kShift) & 3) << 1))) * 16;
+// Two int4 weights (bits 0-3 of each 16-bit half of `shifted`) -> two BF16 values round_bf16((w - z) * scale):
+// one LOP3 plants each nibble in the mantissa of 128.0 (0x4300 | w = 128 + w exactly), one packed subtract of
+// (128 + z) is exact, one packed multiply rounds once - the value the reference computes in FP32 and rounds.
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, uint32_t zero2, uint32_t scale2) {
+  uint32_t planted, difference, product;
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x43004300, 0xea;" : "=r"(planted) : "r"(shifted));
+  asm("sub.bf16x2 %0, %1, %2;" : "=r"(difference) : "r"(planted), "r"(zero2));
+  asm("mul.bf16x2 %0, %1, %2;" : "=r"(product) : "r"(difference), "r"(scale2));
+  return product;
 }
 
-template <bool kAwq>
-__device__ __forceinline__ void stage_activations(const GemmParams& p, unsigned char* lo,
-                                                  unsigned char* hi, bool has_hi, int k0, int kslice) {
-  constexpr int kShift = kAwq ? 3 : 1;
-  const int cells = kslice / 8;
+// BF16 weights are bandwidth-bound, not issue-bound, and a warp covers up to four 64-input units, too many
+// fragments to pin in registers: there the activations sit in shared memory as 16-byte cells of 8 consecutive
+// inputs of one row. Cell (row r < 8, kb) lives at (kb * 8 + (r ^ swizzle(kb))) * 16, rows 8..15 in a second
+// array of the same shape; the swizzle uses the kb bits that differ between the four lanes of a quad so that
+// a quarter-warp's 128-bit loads fall into eight distinct bank groups.
+__device__ __forceinline__ int x_cell(int kb, int r) { return (kb * 8 + (r ^ (((kb >> 1) & 3) << 1))) * 16; }
+
+__device__ __forceinline__ void stage_activations(const GemmParams& p, unsigned char* lo, unsigned char* hi,
+                                                  bool has_hi, int k_begin, int k_count) {
+  const int cells = k_count / 8;
   const int halves = has_hi ? 2 : 1;
   for (int idx = threadIdx.x; idx < cells * 8 * halves; idx += blockDim.x) {
     const int half = idx / (cells * 8);
     const int rem = idx - half * cells * 8;
-    const int r = rem & 7, kb = rem >> 3;
+    const int r = rem & 7, kb = rem >> 3;  // eight lanes write the eight rows of one kb: distinct bank groups
     const int row = r + half * 8;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < p.M) v = *reinterpret_cast<const uint4*>(p.x + size_t(row) * p.x_stride + k0 + kb * 8);
-    if (kAwq) {
-      // (k0k1, k2k3, k4k5, k6k7) -> (k0k4, k1k5, k2k6, k3k7): the pair order int4 extraction yields.
-      uint4 t;
-      t.x = __byte_perm(v.x, v.z, 0x5410);
-      t.y = __byte_perm(v.x, v.z, 0x7632);
-      t.z = __byte_perm(v.y, v.w, 0x5410);
-      t.w = __byte_perm(v.y, v.w, 0x7632);
-      v = t;
-    }
-    *reinterpret_cast<uint4*>((half ? hi : lo) + x_cell<kShift>(kb, r)) = v;
+    if (row < p.M) v = *reinterpret_cast<const uint4*>(p.x + size_t(row) * p.x_stride + k_begin + kb * 8);
+    *reinterpret_cast<uint4*>((half ? hi : lo) + x_cell(kb, r)) = v;
   }
 }
 
-// Registers of one prefetched item for one warp.
-template <bool kAwq, int kTiles, int kUnits>
+// Registers of one prefetched item (one tile) for one warp. Raw loaded words only.
+template <bool kAwq, int kUnits>
 struct ItemRegs {
-  uint4 w[kTiles][kUnits][2];
-  uint32_t scale[kAwq ? kTiles : 1][kAwq ? kUnits : 1];  // BF16 scale replicated in both halves
-  uint32_t zero[kAwq ? kTiles : 1][kAwq ? kUnits : 1];   // BF16 (128 + z) replicated in both halves
+  uint4 w[kUnits][2];
+  uint32_t scale[kAwq ? kUnits : 1];  // BF16 scale of the lane's group (low half)
+  uint32_t zero[kAwq ? kUnits : 1];   // packed zero word holding the lane's group
 };
 
-template <bool kAwq, bool kHigh, int kTiles, int kUnits, int kDepth>
+// A fragments of one 8-input cell: two MMAs' worth of (a0, a1, a2, a3). For int4 weights the 8 inputs are
+// taken in the order (0,4 | 1,5) and (2,6 | 3,7): the pair order the nibble extraction yields.
+template <bool kHigh>
+struct CellFragments {
+  uint32_t a[2][kHigh ? 4 : 2];
+};
+
+template <bool kAwq, bool kHigh>
+__device__ __forceinline__ void load_cell(CellFragments<kHigh>& f, const bf16* x, int x_stride, int M, int g, int k) {
+  uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+  if (g < M) lo = *reinterpret_cast<const uint4*>(x + size_t(g) * x_stride + k);
+  if (kHigh && g + 8 < M) hi = *reinterpret_cast<const uint4*>(x + size_t(g + 8) * x_stride + k);
+  if (kAwq) {
+    // (k0k1, k2k3, k4k5, k6k7) -> (k0k4, k1k5, k2k6, k3k7)
+    uint4 t;
+    t.x = __byte_perm(lo.x, lo.z, 0x5410); t.y = __byte_perm(lo.x, lo.z, 0x7632);
+    t.z = __byte_perm(lo.y, lo.w, 0x5410); t.w = __byte_perm(lo.y, lo.w, 0x7632);
+    lo = t;
+    if (kHigh) {
+      t.x = __byte_perm(hi.x, hi.z, 0x5410); t.y = __byte_perm(hi.x, hi.z, 0x7632);
+      t.z = __byte_perm(hi.y, hi.w, 0x5410); t.w = __byte_perm(hi.y, hi.w, 0x7632);
+      hi = t;
+    }
+  }
+  if (kHigh) {
+    f.a[0][0] = lo.x; f.a[0][1] = hi.x; f.a[0][2] = lo.y; f.a[0][3] = hi.y;
+    f.a[1][0] = lo.z; f.a[1][1] = hi.z; f.a[1][2] = lo.w; f.a[1][3] = hi.w;
+  } else {
+    f.a[0][0] = lo.x; f.a[0][1] = lo.y;
+    f.a[1][0] = lo.z; f.a[1][1] = lo.w;
+  }
+}
+
+template <bool kHigh>
+__device__ __forceinline__ void mma_cell(float (&acc)[4], const CellFragments<kHigh>& f, int which, uint32_t b0,
+                                         uint32_t b1) {
+  if (kHigh)
+    mma_bf16_16816(acc, f.a[which][0], f.a[which][1], f.a[which][2], f.a[which][3], b0, b1);
+  else
+    mma_bf16_16816(acc, f.a[which][0], 0u, f.a[which][1], 0u, b0, b1);
+}
+
+template <bool kAwq, bool kHigh, int kUnits, int kDepth>
 __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const GemmParams p) {
   constexpr int kUnitK = kAwq ? 256 : 64;
-  constexpr int kShift = kAwq ? 3 : 1;
+  constexpr int kCells = kAwq ? 8 : 2;  // 8-input cells a lane owns per unit
+  constexpr int kParts = 4;             // reduction parts per output: a warp's lanes are 4 parts x 8 elements
+  constexpr int kBlock = 136;           // floats per warp in the partial buffer: 128 + 8 keeps loads conflict-free
   extern __shared__ __align__(16) unsigned char smem[];
+  float* part = reinterpret_cast<float*>(smem);  // [2][kGemmWarps][kBlock]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int slice = blockIdx.x % p.ksplit;
   const int group = blockIdx.x / p.ksplit;
   const int groups = gridDim.x / p.ksplit;
-  const int kslice = p.K / p.ksplit;
-  const int k0 = slice * kslice;
-  const int units = kslice / kUnitK;
+  const int units_total = p.K / kUnitK;
+  const int unit_begin = int((long long)slice * units_total / p.ksplit);
+  const int units = int((long long)(slice + 1) * units_total / p.ksplit) - unit_begin;
   const int tiles = p.N / 8;
+  // An item is one tile. The fused SwiGLU epilogue walks (gate tile i, up tile i) as two consecutive items.
   const bool pair = p.epilogue == kEpiSiluPair;
-  const int items = pair ? tiles / 2 : (tiles + kTiles - 1) / kTiles;
-  const int item_begin = int((long long)group * items / groups);
-  const int item_end = int((long long)(group + 1) * items / groups);
+  const int chunks = pair ? tiles / 2 : tiles;
+  const int per_chunk = pair ? 2 : 1;
+  const int item_begin = int((long long)group * chunks / groups) * per_chunk;
+  const int item_end = int((long long)(group + 1) * chunks / groups) * per_chunk;
+  auto tile_of = [&](int item) -> int { return pair ? (item >> 1) + (item & 1) * (tiles / 2) : item; };
 
-  unsigned char* x_lo = smem;
-  unsigned char* x_hi = smem + size_t(kslice) * 16;  // (kslice / 8) cells * 8 rows * 16 B
-  float* part = reinterpret_cast<float*>(smem + size_t(kslice) * 16 * (kHigh ? 2 : 1));
-  // part[2][kGemmWarps][kTiles][32][4]
-
-  auto tile_of = [&](int item, int t) -> int {
-    if (pair) return t == 0 ? item : item + tiles / 2;
-    const int tile = item * kTiles + t;
-    return tile < tiles ? tile : -1;
-  };
-
-  ItemRegs<kAwq, kTiles, kUnits> regs[kDepth];
-
-  auto prefetch = [&](ItemRegs<kAwq, kTiles, kUnits>& r, int item) {
+  // Per-lane bases of everything the lane ever loads for unit j; a tile only adds a row offset.
+  const unsigned char* w_base[kUnits];
+  const unsigned short* s_base[kAwq ? kUnits : 1];
+  const int32_t* z_base[kAwq ? kUnits : 1];
+  int zero_shift[kAwq ? kUnits : 1];
+  bool live[kUnits];
 #pragma unroll
-    for (int t = 0; t < kTiles; ++t) {
-      const int tile = item < item_end ? tile_of(item, t) : -1;
+  for (int j = 0; j < kUnits; ++j) {
+    const int u = warp + kGemmWarps * j;
+    live[j] = u < units;
+    const int k = (unit_begin + (live[j] ? u : 0)) * kUnitK + c * (kUnitK / 4);
+    if (kAwq) {
+      w_base[j] = reinterpret_cast<const unsigned char*>(p.qweight + size_t(g) * (p.K / 8) + k / 8);
+      const int grp = k >> 7;
+      s_base[j] = reinterpret_cast<const unsigned short*>(p.scales) + size_t(g) * p.padded_groups + grp;
+      z_base[j] = p.zeros + size_t(g) * p.zero_stride + (grp >> 3);
+      zero_shift[j] = (grp & 7) * 4;
+    } else {
+      w_base[j] = reinterpret_cast<const unsigned char*>(p.w + size_t(g) * p.ldw + k);
+    }
+  }
+  const size_t w_tile_stride = kAwq ? size_t(8) * (p.K / 8) * 4 : size_t(8) * p.ldw * 2;  // bytes per tile
+
+  ItemRegs<kAwq, kUnits> regs[kDepth];
+  auto prefetch = [&](ItemRegs<kAwq, kUnits>& r, int item) {
+    const bool valid = item < item_end;
+    const int tile = valid ? tile_of(item) : 0;
 #pragma unroll
-      for (int j = 0; j < kUnits; ++j) {
-        const int u = warp + kGemmWarps * j;
-        if (tile >= 0 && u < units) {
-          const size_t n = size_t(tile) * 8 + g;
-          const int k = k0 + u * kUnitK + c * (kUnitK / 4);
-          if (kAwq) {
-            const int32_t* src = p.qweight + n * size_t(p.K / 8) + k / 8;
-            r.w[t][j][0] = ldg_stream(src);
-            r.w[t][j][1] = ldg_stream(src + 4);
-            const int grp = k >> 7;
-            const uint32_t s = __ldg(reinterpret_cast<const unsigned short*>(p.scales) + n * p.padded_groups + grp);
-            const uint32_t zw = uint32_t(__ldg(p.zeros + n * p.zero_stride + (grp >> 3)));
-            r.scale[t][j] = s * 0x10001u;
-            r.zero[t][j] = (0x4300u | ((zw >> ((grp & 7) * 4)) & 15u)) * 0x10001u;
-          } else {
-            const bf16* src = p.w + n * size_t(p.ldw) + k;
-            r.w[t][j][0] = ldg_stream(src);
-            r.w[t][j][1] = ldg_stream(src + 8);
-          }
-        } else {
-          r.w[t][j][0] = make_uint4(0, 0, 0, 0);
-          r.w[t][j][1] = make_uint4(0, 0, 0, 0);
-          if (kAwq) {
-            r.scale[t][j] = 0;
-            r.zero[t][j] = 0x43004300u;
-          }
+    for (int j = 0; j < kUnits; ++j) {
+      if (valid && live[j]) {
+        const unsigned char* src = w_base[j] + size_t(tile) * w_tile_stride;
+        r.w[j][0] = ldg_stream(src);
+        r.w[j][1] = ldg_stream(src + 16);
+        if (kAwq) {
+          r.scale[j] = __ldg(s_base[j] + size_t(tile) * 8 * p.padded_groups);
+          r.zero[j] = uint32_t(__ldg(z_base[j] + size_t(tile) * 8 * p.zero_stride));
+        }
+      } else {
+        r.w[j][0] = make_uint4(0, 0, 0, 0);
+        r.w[j][1] = make_uint4(0, 0, 0, 0);
+        if (kAwq) {
+          r.scale[j] = 0;
+          r.zero[j] = 0;
         }
       }
     }
@@ -193,120 +243,122 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
 #pragma unroll
   for (int s = 0; s < kDepth; ++s) prefetch(regs[s], item_begin + s);
   grid_dependency_wait();
-  stage_activations<kAwq>(p, x_lo, x_hi, kHigh, k0, kslice);
-  __syncthreads();
+
+  // int4: fragments pinned in registers. BF16: activations staged in shared memory behind the partials.
+  CellFragments<kHigh> frag[kAwq ? kUnits : 1][kAwq ? kCells : 1];
+  unsigned char* x_lo = smem + size_t(2) * kGemmWarps * kBlock * sizeof(float);
+  unsigned char* x_hi = x_lo + size_t(units) * kUnitK * 16;
+  if (kAwq) {
+#pragma unroll
+    for (int j = 0; j < kUnits; ++j) {
+      const int u = warp + kGemmWarps * j;
+      const int k = (unit_begin + (live[j] ? u : 0)) * kUnitK + c * (kUnitK / 4);
+#pragma unroll
+      for (int cell = 0; cell < kCells; ++cell)
+        load_cell<kAwq, kHigh>(frag[j][cell], p.x, p.x_stride, live[j] ? p.M : 0, g, k + cell * 8);
+    }
+  } else {
+    stage_activations(p, x_lo, x_hi, kHigh, unit_begin * kUnitK, units * kUnitK);
+    __syncthreads();
+  }
   grid_launch_dependents();
 
+  // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
+  const int e = warp * 8 + (lane & 7);
+  const int part_index = lane >> 3;
+  const int rl = e >> 2, reg = e & 3;
+  const int row = (rl >> 2) + (reg >= 2 ? 8 : 0);
+  const int col = (rl & 3) * 2 + (reg & 1);
   float best_value = -INFINITY;
   int best_index = 0x7fffffff;
+  float gate_sum = 0.0f;  // fused SwiGLU: the gate tile's sum waits here for the up tile
 
   for (int base = item_begin; base < item_end; base += kDepth) {
 #pragma unroll
     for (int s = 0; s < kDepth; ++s) {
       const int item = base + s;
       if (item >= item_end) break;
-      float acc[kTiles][4];
-#pragma unroll
-      for (int t = 0; t < kTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int j = 0; j < kUnits; ++j) {
-        const int u = warp + kGemmWarps * j;
-        if (u < units) {
-          const int kb_base = (u * kUnitK + c * (kUnitK / 4)) >> 3;
+        uint32_t scale2 = 0, zero2 = 0;
+        if (kAwq) {
+          scale2 = regs[s].scale[j] * 0x10001u;
+          zero2 = (0x4300u | ((regs[s].zero[j] >> zero_shift[j]) & 15u)) * 0x10001u;
+        }
 #pragma unroll
-          for (int v = 0; v < 2; ++v) {
+        for (int v = 0; v < 2; ++v) {
+          const uint4 wv = regs[s].w[j][v];
+          if (kAwq) {
 #pragma unroll
-            for (int q = 0; q < (kAwq ? 4 : 1); ++q) {
-              const int kb = kb_base + (kAwq ? v * 4 + q : v);
-              const int cell = x_cell<kShift>(kb, g);
-              const uint4 xa = *reinterpret_cast<const uint4*>(x_lo + cell);
-              uint4 xb = make_uint4(0, 0, 0, 0);
-              if (kHigh) xb = *reinterpret_cast<const uint4*>(x_hi + cell);
-#pragma unroll
-              for (int t = 0; t < kTiles; ++t) {
-                uint32_t b0, b1, b2, b3;
-                if (kAwq) {
-                  const uint4 wv = regs[s].w[t][j][v];
-                  const uint32_t word = q == 0 ? wv.x : q == 1 ? wv.y : q == 2 ? wv.z : wv.w;
-                  const __nv_bfloat162 zero = *reinterpret_cast<const __nv_bfloat162*>(&regs[s].zero[t][j]);
-                  const __nv_bfloat162 scale = *reinterpret_cast<const __nv_bfloat162*>(&regs[s].scale[t][j]);
-                  uint32_t e0 = (word & 0x000f000fu) | 0x43004300u;
-                  uint32_t e1 = ((word >> 4) & 0x000f000fu) | 0x43004300u;
-                  uint32_t e2 = ((word >> 8) & 0x000f000fu) | 0x43004300u;
-                  uint32_t e3 = ((word >> 12) & 0x000f000fu) | 0x43004300u;
-                  __nv_bfloat162 d0 = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&e0), zero), scale);
-                  __nv_bfloat162 d1 = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&e1), zero), scale);
-                  __nv_bfloat162 d2 = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&e2), zero), scale);
-                  __nv_bfloat162 d3 = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&e3), zero), scale);
-                  b0 = *reinterpret_cast<uint32_t*>(&d0);
-                  b1 = *reinterpret_cast<uint32_t*>(&d1);
-                  b2 = *reinterpret_cast<uint32_t*>(&d2);
-                  b3 = *reinterpret_cast<uint32_t*>(&d3);
-                } else {
-                  const uint4 wv = regs[s].w[t][j][v];
-                  b0 = wv.x; b1 = wv.y; b2 = wv.z; b3 = wv.w;
-                }
-                mma_bf16_16816(acc[t], xa.x, xb.x, xa.y, xb.y, b0, b1);
-                mma_bf16_16816(acc[t], xa.z, xb.z, xa.w, xb.w, b2, b3);
-              }
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t word = q == 0 ? wv.x : q == 1 ? wv.y : q == 2 ? wv.z : wv.w;
+              const uint32_t b0 = dequant_pair(word, zero2, scale2);
+              const uint32_t b1 = dequant_pair(word >> 4, zero2, scale2);
+              const uint32_t b2 = dequant_pair(word >> 8, zero2, scale2);
+              const uint32_t b3 = dequant_pair(word >> 12, zero2, scale2);
+              mma_cell<kHigh>(acc, frag[j][v * 4 + q], 0, b0, b1);
+              mma_cell<kHigh>(acc, frag[j][v * 4 + q], 1, b2, b3);
             }
+          } else if (live[j]) {
+            // Cell of (unit, lane, v); both cells of a lane share the swizzle term.
+            const int u = warp + kGemmWarps * j;
+            const int cell = x_cell((u * kUnitK + c * (kUnitK / 4)) >> 3, g) + v * 128;
+            const uint4 xa = *reinterpret_cast<const uint4*>(x_lo + cell);
+            uint4 xb = make_uint4(0, 0, 0, 0);
+            if (kHigh) xb = *reinterpret_cast<const uint4*>(x_hi + cell);
+            mma_bf16_16816(acc, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
+            mma_bf16_16816(acc, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
           }
         }
       }
       // This register set is free again: refill it with the item kDepth ahead.
       prefetch(regs[s], item + kDepth);
 
-      float* mine = part + ((size_t(item & 1) * kGemmWarps + warp) * kTiles) * 128;
-#pragma unroll
-      for (int t = 0; t < kTiles; ++t)
-        *reinterpret_cast<float4*>(mine + t * 128 + lane * 4) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+      // part[buffer][warp][e] with e = lane * 4 + reg (conflict-free 128-bit stores).
+      float* mine = part + (size_t(item & 1) * kGemmWarps + warp) * kBlock;
+      *reinterpret_cast<float4*>(mine + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       __syncthreads();
 
-      const int reducers = (pair ? 1 : kTiles) * 128;
-      if (int(threadIdx.x) < reducers) {
-        const int t = threadIdx.x >> 7;
-        const int e = threadIdx.x & 127;
-        const int rl = e >> 2, reg = e & 3;
-        const int row = (rl >> 2) + (reg >= 2 ? 8 : 0);
-        const int col = (rl & 3) * 2 + (reg & 1);
-        const float* src = part + size_t(item & 1) * kGemmWarps * kTiles * 128 + e;
-        if (pair) {
-          float gate = 0.0f, up = 0.0f;
+      // Fixed-order reduction by all 16 warps: part p adds the partials of warps p, p + 4, p + 8, p + 12 in
+      // that order and the parts are combined by two shuffles, so an output sees the same additions in every
+      // run. The 136-float stride puts the 32 lanes of each load in 32 different banks.
+      float sum = 0.0f;
+      {
+        const float* src = part + (size_t(item & 1) * kGemmWarps + part_index) * kBlock + e;
 #pragma unroll
-          for (int w = 0; w < kGemmWarps; ++w) {
-            gate += src[(w * kTiles + 0) * 128];
-            up += src[(w * kTiles + 1) * 128];
-          }
-          if (row < p.M) {
-            const int n = item * 8 + col;
+        for (int w = 0; w < kGemmWarps / kParts; ++w) sum += src[size_t(w) * kParts * kBlock];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      if (part_index == 0 && row < p.M) {
+        const int tile = tile_of(item);
+        const int n = tile * 8 + col;
+        if (pair) {
+          if ((item & 1) == 0) {
+            gate_sum = sum;
+          } else {
+            float gate = gate_sum, up = sum;
+            const int out_n = n - p.N / 2;
             if (p.bias) {
-              gate += __bfloat162float(p.bias[n]);
-              up += __bfloat162float(p.bias[n + p.N / 2]);
+              gate += __bfloat162float(p.bias[out_n]);
+              up += __bfloat162float(p.bias[n]);
             }
-            p.out[size_t(row) * p.out_stride + n] =
+            p.out[size_t(row) * p.out_stride + out_n] =
                 __float2bfloat16_rn(silu_multiply_value(round_bf16(gate), round_bf16(up)));
           }
+        } else if (p.epilogue == kEpiPartial) {
+          p.partial[(size_t(slice) * p.M + row) * p.N + n] = sum;
         } else {
-          const int tile = tile_of(item, t);
-          float sum = 0.0f;
-#pragma unroll
-          for (int w = 0; w < kGemmWarps; ++w) sum += src[(w * kTiles + t) * 128];
-          if (tile >= 0 && row < p.M && (kHigh || reg < 2)) {
-            const int n = tile * 8 + col;
-            if (p.epilogue == kEpiPartial) {
-              p.partial[(size_t(slice) * p.M + row) * p.N + n] = sum;
-            } else {
-              if (p.bias) sum += __bfloat162float(p.bias[n]);
-              const bf16 rounded = __float2bfloat16_rn(sum);
-              p.out[size_t(row) * p.out_stride + n] = rounded;
-              if (p.epilogue == kEpiArgmax) {
-                float value = __bfloat162float(rounded);
-                if (isnan(value)) value = -INFINITY;
-                if (value > best_value || (value == best_value && n < best_index)) {
-                  best_value = value;
-                  best_index = n;
-                }
-              }
+          if (p.bias) sum += __bfloat162float(p.bias[n]);
+          const bf16 rounded = __float2bfloat16_rn(sum);
+          p.out[size_t(row) * p.out_stride + n] = rounded;
+          if (p.epilogue == kEpiArgmax) {
+            float value = __bfloat162float(rounded);
+            if (isnan(value)) value = -INFINITY;
+            if (value > best_value || (value == best_value && n < best_index)) {
+              best_value = value;
+              best_index = n;
             }
           }
         }
@@ -315,32 +367,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
   }
 
   if (p.epilogue == kEpiArgmax) {
-    // Reducer thread (t, e) always owns the same output row; fold the kTiles * 8 owners of a row.
+    // An element owner always sees the same output row; fold the 8 owners of each row.
     __syncthreads();
     float* values = part;
-    int* indices = reinterpret_cast<int*>(part + kTiles * 128);
-    if (int(threadIdx.x) < kTiles * 128) {
-      values[threadIdx.x] = best_value;
-      indices[threadIdx.x] = best_index;
+    int* indices = reinterpret_cast<int*>(part + 128);
+    if (part_index == 0) {
+      values[e] = best_value;
+      indices[e] = best_index;
     }
     __syncthreads();
     if (threadIdx.x < 16) {
-      const int row = threadIdx.x;
+      const int want = threadIdx.x;
       float bv = -INFINITY;
       int bi = 0x7fffffff;
-      for (int t = 0; t < kTiles; ++t)
-        for (int e = 0; e < 128; ++e) {
-          const int rl = e >> 2, reg = e & 3;
-          if ((rl >> 2) + (reg >= 2 ? 8 : 0) != row) continue;
-          const float value = values[t * 128 + e];
-          const int index = indices[t * 128 + e];
-          if (value > bv || (value == bv && index < bi)) {
-            bv = value;
-            bi = index;
-          }
+      for (int v = 0; v < 128; ++v) {
+        const int vl = v >> 2, vr = v & 3;
+        if ((vl >> 2) + (vr >= 2 ? 8 : 0) != want) continue;
+        const float value = values[v];
+        const int index = indices[v];
+        if (value > bv || (value == bv && index < bi)) {
+          bv = value;
+          bi = index;
         }
-      p.best_value[blockIdx.x * 16 + row] = bv;
-      p.best_index[blockIdx.x * 16 + row] = bi;
+      }
+      p.best_value[blockIdx.x * 16 + want] = bv;
+      p.best_index[blockIdx.x * 16 + want] = bi;
     }
   }
 }
@@ -361,7 +412,8 @@ __global__ void dense_generic_kernel(const bf16* x, int x_stride, const bf16* w,
 struct GemmPlan {
   bool fast = false;
   bool high = false;
-  int tiles_per_item = 1, units_per_warp = 1, depth = 2;
+  int units_per_warp = 1;
+  int tiles_per_block = 0;  // int4 path: tiles (items) the busiest block walks
   int ksplit = 1, grid = 1;
   size_t smem = 0;
 };
