@@ -1,31 +1,54 @@
-// int4 (AWQ, group 128) small-M GEMM with bulk-copy staging: out[M,N] = x[M,K] * dequant(W)[N,K]^T (+ bias).
+// int4 (AWQ, group 128) small-M GEMM fed by TMA: out[M,N] = x[M,K] * dequant(W)[N,K]^T (+ bias).
 //
-// A tile is 8 output features = 8 consecutive rows of the N-major packed weight matrix. Each row slice is
-// brought into shared memory by one asynchronous bulk copy (cp.async.bulk, the 1-D form of TMA) that
-// completes on an mbarrier; a ring of kStages tiles is always in flight per block, so HBM streams
-// continuously and independently of the warps' register scoreboards, and the loop issues no global loads.
-// Row slices land with a 16-byte skew between rows, which makes the warps' 128-bit reads conflict-free.
-// The group scales and zero points of every tile the block will touch are fetched once into shared memory
-// before the kernel waits for its predecessor, as are the first kStages tiles: weights do not depend on it.
+// A tile is 8 output features = 8 consecutive rows of the N-major packed weight matrix, over one K slice of
+// up to 4096 inputs. One thread brings a whole tile into shared memory with a single tiled TMA copy
+// (cp.async.bulk.tensor) that completes on an mbarrier, and with two more small copies for the tile's group
+// scales and packed zero points; a ring of tiles is always in flight per block, so HBM streams continuously,
+// independently of the warps' register scoreboards, and the loop issues no global loads at all.
 //
-// The <= 16 activation rows never change while the block runs and warp w always works on input features
+// The weight matrix is described to TMA as a rank-3 tensor [unit of 256 inputs][row][128 bytes], so that the
+// staged tile is [unit][row][128 B] and the 128-byte swizzle places the 16-byte chunk j of row r at chunk
+// (j ^ r): the eight rows a quarter-warp reads in one 128-bit load then fall into eight distinct bank groups.
+//
+// The <= 16 activation rows never change while the block runs and warp w always works on inputs
 // [256 w, 256 w + 256) of the block's K slice, so its A fragments are loaded once, in the register order
 // mma.sync wants, and stay in registers: the inner loop is nibble extraction, the exact BF16 dequantisation
 // (see dequant_pair) and mma.sync.m16n8k16 with FP32 accumulation. Per tile the 16 warps add their partial
 // accumulators through shared memory in a fixed order. K beyond 4096 is split over blocks (ksplit) that write
 // FP32 partials for a separate fixed-order reduction.
 //
+// Scale and zero-point rows that TMA cannot address (row pitch not a multiple of 16 bytes) are instead
+// fetched once, with ordinary loads, for every tile the block will touch, before the kernel waits for its
+// predecessor.
+//
 // Every wait on an mbarrier is bounded: if a copy does not complete within the limit the block records the
 // failure in GemmParams::status and leaves without touching its outputs again.
 #pragma once
+
+#include <cuda.h>
 
 #include "smallm_gemm.cuh"
 
 namespace ei {
 
-constexpr int kAwqStages = 8;
-constexpr int kAwqRowSkew = 16;          // bytes added to each staged row
+constexpr int kAwqMaxStages = 10;
+constexpr int kAwqSliceUnits = 16;            // 256-input units per K slice: one per warp
 constexpr uint32_t kAwqWaitLimit = 1u << 22;  // polls of ~100 ns before a wait gives up
+
+struct AwqTensorMaps {
+  CUtensorMap weights;  // u64 [units][N][16], box [units_box][8][16], 128-byte swizzle
+  CUtensorMap scales;   // bf16 [N][padded_groups], box [8][scale_box]
+  CUtensorMap zeros;    // i32 [N][zero_stride], box [8][zero_box]
+};
+
+struct AwqLaunch {
+  int tiles_per_block;  // tiles (items) the busiest block walks
+  int stages;           // tiles in flight per block
+  int units_box;        // units the weight box covers (<= 16)
+  int tma_sz;           // 1: scales/zeros ride with the tile by TMA; 0: fetched up front by ordinary loads
+  int scale_box;        // groups per staged scale row
+  int zero_box;         // words per staged zero row
+};
 
 __device__ __forceinline__ uint32_t smem_address(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -54,46 +77,58 @@ __device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity) {
     if (mbarrier_try_wait(bar, parity)) return true;
   return false;
 }
-__device__ __forceinline__ void bulk_copy_to_shared(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_address(dst)),
-               "l"(src), "r"(bytes), "r"(smem_address(bar))
-               : "memory");
+// Tiled TMA loads; coordinates run from the innermost dimension outwards. x times the element size must be
+// a multiple of 16 bytes (the callers below only pass multiples of whole slices).
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(smem_address(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_address(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], "
+      "[%5];" ::"r"(smem_address(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_address(bar))
+      : "memory");
 }
 
-struct AwqStreamLayout {
-  int row_bytes;     // staged bytes per weight row (slice) incl. skew
-  int stage_bytes;   // 8 rows
-  int groups;        // scale groups of the slice
-  int sz_tile_bytes; // scales + zero nibbles of one tile: 8 rows x groups x (2 + 1) bytes, 16-byte padded
+struct AwqLayout {
+  int weight_bytes;   // staged weight bytes of a tile: units_box KiB
+  int stage_bytes;    // weights + 1 KiB for the tile's scales (512 B) and zero points (128 B)
+  int sz_tile_bytes;  // up-front mode: scales + zero nibbles of one tile, 16-byte padded
   size_t part_offset, barrier_offset, sz_offset, stage_offset, total;
 };
 
-__host__ __device__ inline AwqStreamLayout awq_stream_layout(int units, int tiles_per_block) {
-  AwqStreamLayout l;
-  l.row_bytes = units * 128 + kAwqRowSkew;
-  l.stage_bytes = 8 * l.row_bytes;
-  l.groups = units * 2;
-  l.sz_tile_bytes = ((8 * l.groups * 3) + 15) & ~15;
-  l.part_offset = 0;
-  l.barrier_offset = size_t(4) * kGemmWarps * 136 * sizeof(float);  // two buffers x two tiles of partials
+// Offsets are relative to the first 1024-byte boundary of the dynamic shared memory (the swizzle needs it);
+// `total` includes the slack to reach that boundary.
+__host__ __device__ inline AwqLayout awq_layout(const AwqLaunch& cfg) {
+  AwqLayout l;
+  l.weight_bytes = cfg.units_box * 1024;
+  l.stage_bytes = l.weight_bytes + 1024;
+  l.sz_tile_bytes = cfg.tma_sz ? 0 : ((8 * cfg.units_box * 2 * 3) + 15) & ~15;
+  l.stage_offset = 0;
+  l.part_offset = size_t(cfg.stages) * l.stage_bytes;
+  l.barrier_offset = l.part_offset + size_t(4) * kGemmWarps * 136 * sizeof(float);  // 2 buffers x 2 tiles
   l.sz_offset = l.barrier_offset + 128;
-  l.stage_offset = (l.sz_offset + size_t(tiles_per_block) * l.sz_tile_bytes + 127) & ~size_t(127);
-  l.total = l.stage_offset + size_t(kAwqStages) * l.stage_bytes;
+  l.total = l.sz_offset + size_t(cfg.tiles_per_block) * l.sz_tile_bytes + 1024;
   return l;
 }
 
 template <bool kHigh>
-__global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmParams p, int tiles_per_block) {
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    awq_tma_kernel(const __grid_constant__ AwqTensorMaps maps, const GemmParams p, const AwqLaunch cfg) {
   constexpr int kBlock = 136;
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_address(smem_raw) & 1023u)) & 1023u);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int slice = blockIdx.x % p.ksplit;
   const int group = blockIdx.x / p.ksplit;
   const int groups = gridDim.x / p.ksplit;
   const int units_total = p.K / 256;
-  const int unit_begin = int((long long)slice * units_total / p.ksplit);
-  const int units = int((long long)(slice + 1) * units_total / p.ksplit) - unit_begin;
+  const int unit_begin = slice * kAwqSliceUnits;
+  const int units = min(kAwqSliceUnits, units_total - unit_begin);
   const int tiles = p.N / 8;
   const bool pair = p.epilogue == kEpiSiluPair;
   const int chunks = pair ? tiles / 2 : tiles;
@@ -103,41 +138,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmP
   const int item_count = item_end - item_begin;
   auto tile_of = [&](int item) -> int { return pair ? (item >> 1) + (item & 1) * (tiles / 2) : item; };
 
-  const AwqStreamLayout layout = awq_stream_layout(units, tiles_per_block);
+  const AwqLayout layout = awq_layout(cfg);
+  unsigned char* stages = smem + layout.stage_offset;
   float* part = reinterpret_cast<float*>(smem + layout.part_offset);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + layout.barrier_offset);
   unsigned char* sz = smem + layout.sz_offset;
-  unsigned char* stages = smem + layout.stage_offset;
-  const uint32_t slice_row_bytes = uint32_t(units) * 128;
-  const unsigned char* weight_rows = reinterpret_cast<const unsigned char*>(p.qweight) + size_t(unit_begin) * 128;
-  const size_t weight_row_stride = size_t(p.K / 8) * 4;
+  const int scale_pitch = cfg.scale_box * 2, zero_pitch = cfg.zero_box * 4;
+  const uint32_t tile_bytes = uint32_t(layout.weight_bytes) + (cfg.tma_sz ? 8u * (scale_pitch + zero_pitch) : 0u);
 
-  // Lanes 0-7 of warp 0 each copy one row of the tile; lane 0 announces the bytes first.
+  // One thread brings in a whole tile.
   auto issue = [&](int index) {
     if (index >= item_count) return;
-    const int stage = index % kAwqStages;
-    const int tile = tile_of(item_begin + index);
-    if (lane == 0) mbarrier_expect_tx(&full[stage], 8 * slice_row_bytes);
-    __syncwarp();
-    if (lane < 8)
-      bulk_copy_to_shared(stages + size_t(stage) * layout.stage_bytes + lane * layout.row_bytes,
-                          weight_rows + (size_t(tile) * 8 + lane) * weight_row_stride, slice_row_bytes, &full[stage]);
+    const int stage = index % cfg.stages;
+    const int row = tile_of(item_begin + index) * 8;
+    unsigned char* dst = stages + size_t(stage) * layout.stage_bytes;
+    mbarrier_expect_tx(&full[stage], tile_bytes);
+    tma_load_3d(dst, &maps.weights, 0, row, unit_begin, &full[stage]);
+    if (cfg.tma_sz) {
+      tma_load_2d(dst + layout.weight_bytes, &maps.scales, unit_begin * 2, row, &full[stage]);
+      tma_load_2d(dst + layout.weight_bytes + 512, &maps.zeros, unit_begin / 4, row, &full[stage]);
+    }
   };
-
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kAwqStages; ++s) mbarrier_init(&full[s], 1);
+    for (int s = 0; s < cfg.stages; ++s) mbarrier_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int s = 0; s < cfg.stages; ++s) issue(s);
   }
-  __syncthreads();
-  if (warp == 0)
-    for (int s = 0; s < kAwqStages; ++s) issue(s);
-
-  // Scales (BF16) and zero nibbles (one byte each) of every tile of this block: [item][row][group].
-  // Four elements per thread per round, all eight loads issued before the first store, so a round costs one
-  // memory latency.
-  {
-    const int per_tile = 8 * layout.groups;
+  if (!cfg.tma_sz) {
+    // Scales (BF16) and zero nibbles (one byte each) of every tile of this block: [item][row][group].
+    // Four elements per thread per round, all eight loads issued before the first store, so a round costs
+    // one memory latency.
+    const int slice_groups = cfg.units_box * 2;
+    const int per_tile = 8 * slice_groups;
     const int total = item_count * per_tile;
+    const int last_group = p.K / 128 - 1;
     for (int first = threadIdx.x; first < total; first += 4 * blockDim.x) {
       unsigned short scale[4];
       uint32_t zero_word[4];
@@ -150,7 +185,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmP
         shift[k] = 0;
         if (idx < total) {
           const int index = idx / per_tile, rem = idx - index * per_tile;
-          const int r = rem / layout.groups, grp = unit_begin * 2 + (rem - r * layout.groups);
+          const int r = rem / slice_groups, grp = min(unit_begin * 2 + (rem - r * slice_groups), last_group);
           const size_t n = size_t(tile_of(item_begin + index)) * 8 + r;
           scale[k] = __ldg(reinterpret_cast<const unsigned short*>(p.scales) + n * p.padded_groups + grp);
           zero_word[k] = uint32_t(__ldg(p.zeros + n * p.zero_stride + (grp >> 3)));
@@ -180,7 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmP
     for (int cell = 0; cell < 8; ++cell)
       load_cell<true, kHigh>(frag[cell], p.x, p.x_stride, live ? p.M : 0, g, k + cell * 8);
   }
-  __syncthreads();  // scales / zeros visible
+  __syncthreads();  // barriers initialised; up-front scales / zeros visible
   grid_launch_dependents();
 
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
@@ -190,19 +225,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmP
   const int row = (rl >> 2) + (reg >= 2 ? 8 : 0);
   const int col = (rl & 3) * 2 + (reg & 1);
   const int lane_group = warp * 2 + (c >> 1);  // this lane's scale group within the slice
+  // This lane's two 16-byte chunks of row g of unit `warp`, after the 128-byte swizzle.
+  const int chunk0 = warp * 1024 + g * 128 + (((2 * c) ^ g) << 4);
+  const int chunk1 = warp * 1024 + g * 128 + (((2 * c + 1) ^ g) << 4);
 
   // One tile: 8 words per lane, two accumulator chains so consecutive MMAs do not wait on each other.
   auto compute_tile = [&](int index, float (&acc)[4]) {
     float other[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
     if (!live) return;
-    const int stage = index % kAwqStages;
-    const unsigned char* tile_sz = sz + size_t(index) * layout.sz_tile_bytes;
-    const uint32_t scale2 = uint32_t(reinterpret_cast<const unsigned short*>(tile_sz)[g * layout.groups + lane_group]) * 0x10001u;
-    const uint32_t zero2 = (0x4300u | tile_sz[8 * layout.groups * 2 + g * layout.groups + lane_group]) * 0x10001u;
-    const unsigned char* src = stages + size_t(stage) * layout.stage_bytes + g * layout.row_bytes + warp * 128 + c * 32;
-    const uint4 w0 = *reinterpret_cast<const uint4*>(src);
-    const uint4 w1 = *reinterpret_cast<const uint4*>(src + 16);
+    const unsigned char* tile = stages + size_t(index % cfg.stages) * layout.stage_bytes;
+    uint32_t scale2, zero2;
+    if (cfg.tma_sz) {
+      const unsigned char* tail = tile + layout.weight_bytes;
+      const uint32_t zero_word = *reinterpret_cast<const uint32_t*>(tail + 512 + g * zero_pitch + (lane_group >> 3) * 4);
+      scale2 = uint32_t(*reinterpret_cast<const unsigned short*>(tail + g * scale_pitch + lane_group * 2)) * 0x10001u;
+      zero2 = (0x4300u | ((zero_word >> ((lane_group & 7) * 4)) & 15u)) * 0x10001u;
+    } else {
+      const int slice_groups = cfg.units_box * 2;
+      const unsigned char* tile_sz = sz + size_t(index) * layout.sz_tile_bytes;
+      scale2 = uint32_t(reinterpret_cast<const unsigned short*>(tile_sz)[g * slice_groups + lane_group]) * 0x10001u;
+      zero2 = (0x4300u | tile_sz[8 * slice_groups * 2 + g * slice_groups + lane_group]) * 0x10001u;
+    }
+    const uint4 w0 = *reinterpret_cast<const uint4*>(tile + chunk0);
+    const uint4 w1 = *reinterpret_cast<const uint4*>(tile + chunk1);
 #pragma unroll
     for (int cell = 0; cell < 8; ++cell) {
       const uint4 wv = cell < 4 ? w0 : w1;
@@ -219,11 +265,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmP
   };
 
   auto wait_tile = [&](int index) -> bool {
-#ifdef EI_EXP_NOWAIT
-    return true;
-#else
-    return mbarrier_wait(&full[index % kAwqStages], (index / kAwqStages) & 1);
-#endif
+    return mbarrier_wait(&full[index % cfg.stages], (index / cfg.stages) & 1);
   };
 
   // Two tiles per block-wide barrier.
@@ -244,10 +286,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_stream_kernel(const GemmP
     *reinterpret_cast<float4*>(mine + lane * 4) = make_float4(acc0[0], acc0[1], acc0[2], acc0[3]);
     *reinterpret_cast<float4*>(mine + kGemmWarps * kBlock + lane * 4) = make_float4(acc1[0], acc1[1], acc1[2], acc1[3]);
     __syncthreads();
-    // Every warp has finished reading these two stages: refill them with the tiles kStages ahead.
-    if (warp == 0) {
-      issue(index + kAwqStages);
-      issue(index + 1 + kAwqStages);
+    // Every warp has finished reading these two stages: refill them with the tiles `stages` ahead.
+    if (threadIdx.x == 0) {
+      issue(index + cfg.stages);
+      issue(index + 1 + cfg.stages);
     }
     float sums[2];
 #pragma unroll

@@ -1,7 +1,9 @@
 // Dispatch, planning and fallbacks for the small-M weight-streaming GEMM.
-#include "awq_stream.cuh"
+#include "awq_tma.cuh"
 
 #include <algorithm>
+#include <stdexcept>
+#include <string>
 
 namespace ei {
 
@@ -107,7 +109,10 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
   if (awq) {
     if (epilogue == kEpiArgmax) return plan;  // the vocabulary head is a dense matrix
     plan.tiles_per_block = ((chunks + groups - 1) / groups) * (pair ? 2 : 1);
-    smem = awq_stream_layout(units, plan.tiles_per_block).total;
+    // Feasible if two tiles fit in flight even when scales and zero points are staged up front.
+    AwqLaunch worst{plan.tiles_per_block, 2, std::min(kAwqSliceUnits, units_total), 0, 0, 0};
+    smem = awq_layout(worst).total;
+    plan.smem_limit = smem_limit;
   }
   if (smem > smem_limit) return plan;
   plan.fast = true;
@@ -118,27 +123,96 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
   return plan;
 }
 
-void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
-  const int U = plan.units_per_warp;
-  if (awq) {
-    static thread_local int configured_device = -1;
-    int device = 0;
-    EI_CUDA(cudaGetDevice(&device));
-    if (configured_device != device) {
-      EI_CUDA(cudaFuncSetAttribute(awq_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      EI_CUDA(cudaFuncSetAttribute(awq_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      configured_device = device;
-    }
-    if (plan.high)
-      launch(awq_stream_kernel<true>, dim3(plan.grid), dim3(kGemmThreads), plan.smem, stream, pdl, p, plan.tiles_per_block);
-    else
-      launch(awq_stream_kernel<false>, dim3(plan.grid), dim3(kGemmThreads), plan.smem, stream, pdl, p, plan.tiles_per_block);
-    return;
-  } else {
-    if (U == 1) return launch_high<false, 1, 6, 6>(plan, p, stream, pdl);
-    if (U == 2) return launch_high<false, 2, 4, 4>(plan, p, stream, pdl);
-    if (U == 4) return launch_high<false, 4, 2, 2>(plan, p, stream, pdl);
+namespace {
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library does not link libcuda.
+EncodeTiled tensor_map_encoder() {
+  static const EncodeTiled encoder = [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+    const cudaError_t status = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found);
+    if (status != cudaSuccess || found != cudaDriverEntryPointSuccess || !entry)
+      throw std::runtime_error("The CUDA driver does not provide cuTensorMapEncodeTiled");
+    return reinterpret_cast<EncodeTiled>(entry);
+  }();
+  return encoder;
+}
+
+void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
+                const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle, const char* what) {
+  const cuuint32_t ones[3] = {1, 1, 1};
+  const CUresult result = tensor_map_encoder()(map, type, cuuint32_t(rank), const_cast<void*>(base), dims, strides, box,
+                                               ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (result != CUDA_SUCCESS)
+    throw std::runtime_error(std::string("Tensor map for AWQ ") + what + " could not be encoded: " +
+                             std::to_string(int(result)));
+}
+
+bool aligned_16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, bool pdl) {
+  const int units_total = p.K / 256;
+  AwqLaunch cfg{};
+  cfg.tiles_per_block = plan.tiles_per_block;
+  cfg.units_box = std::min(kAwqSliceUnits, units_total);
+  // TMA needs 16-byte aligned bases and row pitches.
+  cfg.tma_sz = aligned_16(p.scales) && aligned_16(p.zeros) && p.padded_groups % 8 == 0 && p.zero_stride % 4 == 0;
+  cfg.scale_box = cfg.tma_sz ? std::min(32, p.padded_groups) : 0;
+  cfg.zero_box = cfg.tma_sz ? std::min(4, p.zero_stride) : 0;
+  cfg.stages = kAwqMaxStages;
+  while (cfg.stages > 2 && awq_layout(cfg).total > plan.smem_limit) --cfg.stages;
+  const size_t smem = awq_layout(cfg).total;
+  if (smem > plan.smem_limit) throw std::invalid_argument("small-M int4 GEMM does not fit in shared memory");
+
+  AwqTensorMaps maps{};
+  {
+    // Packed weights as [unit of 256 inputs][row][32 words]: a box is one tile, staged as [unit][row][128 B].
+    const cuuint64_t dims[3] = {32, cuuint64_t(p.N), cuuint64_t(units_total)};
+    const cuuint64_t strides[2] = {cuuint64_t(p.K / 8) * 4, 128};
+    const cuuint32_t box[3] = {32, 8, cuuint32_t(cfg.units_box)};
+    encode_map(&maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.qweight, dims, strides, box,
+               CU_TENSOR_MAP_SWIZZLE_128B, "weights");
   }
+  if (cfg.tma_sz) {
+    const cuuint64_t scale_dims[2] = {cuuint64_t(p.padded_groups), cuuint64_t(p.N)};
+    const cuuint64_t scale_strides[1] = {cuuint64_t(p.padded_groups) * 2};
+    const cuuint32_t scale_box[2] = {cuuint32_t(cfg.scale_box), 8};
+    encode_map(&maps.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, p.scales, scale_dims, scale_strides, scale_box,
+               CU_TENSOR_MAP_SWIZZLE_NONE, "scales");
+    const cuuint64_t zero_dims[2] = {cuuint64_t(p.zero_stride), cuuint64_t(p.N)};
+    const cuuint64_t zero_strides[1] = {cuuint64_t(p.zero_stride) * 4};
+    const cuuint32_t zero_box[2] = {cuuint32_t(cfg.zero_box), 8};
+    encode_map(&maps.zeros, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.zeros, zero_dims, zero_strides, zero_box,
+               CU_TENSOR_MAP_SWIZZLE_NONE, "zero points");
+  }
+
+  static thread_local int configured_device = -1;
+  int device = 0;
+  EI_CUDA(cudaGetDevice(&device));
+  if (configured_device != device) {
+    EI_CUDA(cudaFuncSetAttribute(awq_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    EI_CUDA(cudaFuncSetAttribute(awq_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_device = device;
+  }
+  if (plan.high)
+    launch(awq_tma_kernel<true>, dim3(plan.grid), dim3(kGemmThreads), smem, stream, pdl, maps, p, cfg);
+  else
+    launch(awq_tma_kernel<false>, dim3(plan.grid), dim3(kGemmThreads), smem, stream, pdl, maps, p, cfg);
+}
+
+}  // namespace
+
+void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
+  if (awq) return launch_awq(plan, p, stream, pdl);
+  const int U = plan.units_per_warp;
+  if (U == 1) return launch_high<false, 1, 6, 6>(plan, p, stream, pdl);
+  if (U == 2) return launch_high<false, 2, 4, 4>(plan, p, stream, pdl);
+  if (U == 4) return launch_high<false, 4, 2, 2>(plan, p, stream, pdl);
   throw std::invalid_argument("small-M GEMM plan has no kernel instance");
 }
 

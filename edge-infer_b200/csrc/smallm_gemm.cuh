@@ -414,6 +414,7 @@ struct GemmPlan {
   bool high = false;
   int units_per_warp = 1;
   int tiles_per_block = 0;  // int4 path: tiles (items) the busiest block walks
+  size_t smem_limit = 0;    // int4 path: dynamic shared memory a block may opt in to
   int ksplit = 1, grid = 1;
   size_t smem = 0;
 };

