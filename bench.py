@@ -316,14 +316,9 @@ def run_native(args, rank: int, world: int, local_rank: int):
     if dist:
         dist.barrier()
 
-    totals = torch.tensor([float(emitted), float(e2e_emitted)], dtype=torch.float64, device="cuda")
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device="cuda")
-    if dist:
-        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    totals, times = totals.cpu().numpy(), times.cpu().numpy()
-    value = totals[0] / (times[0] * 1e-3)
-    e2e_value = totals[1] / (times[1] * 1e-3)
+    totals, times = package.sharding.aggregate(dist, torch, [emitted, e2e_emitted], [elapsed_ms, e2e_ms], "cuda")
+    value = package.sharding.throughput(totals[0], times[0])
+    e2e_value = package.sharding.throughput(totals[1], times[1])
     ms_per_step = times[0] / args.steps
 
     if rank == 0:

@@ -9,7 +9,7 @@ modules here are its host-side mirror for tests and benchmarks:
 The directory name is not an importable identifier; load it as `edge_infer_b200`
 (see __graft_entry__.load_package()).
 """
-from . import abi, operators, runtime, synthetic  # noqa: F401
+from . import abi, operators, runtime, sharding, synthetic  # noqa: F401
 from .runtime import Model, Session, Shape  # noqa: F401
 
 __all__ = ["abi", "operators", "runtime", "synthetic", "Model", "Session", "Shape"]
