@@ -115,6 +115,7 @@ PROTOTYPES = {
     "ei_attention_scratch_bytes": (_Z, [_Z, _Z, _Z, _Z]),
     "ei_attention_prefill_bf16": (_S, [C.POINTER(Context), View3, View3, View3, View3, _Z, _P, _Z]),
     "ei_attention_verify_bf16": (_S, [C.POINTER(Context), View3, View3, View3, View3, _P, _P, _Z]),
+    "ei_attention_prefill_static_bf16": (_S, [C.POINTER(Context), View3, View3, View3, View3, _Z]),
     "ei_sample_scratch_bytes": (_Z, [_Z, _Z]),
     "ei_sample_greedy_bf16": (_S, [C.POINTER(Context), View2, View1, _P, _Z]),
     "ei_verify_accept": (_S, [C.POINTER(Context), _P, _P, _Z, _P, _P, _P]),

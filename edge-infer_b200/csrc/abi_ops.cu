@@ -6,6 +6,8 @@
 #include "smallm_gemm.cuh"
 
 #include <cmath>
+#include <mutex>
+#include <string>
 #include <limits>
 
 namespace ei {
@@ -438,6 +440,54 @@ ei_status ei_attention_verify_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k
   return guarded([&] {
     if (!device_offset) throw std::invalid_argument("Verify attention requires a device offset");
     run_attention(ctx, q, k_capacity, v_capacity, out, 0, device_offset, scratch, scratch_bytes);
+  });
+}
+
+// ---- attention for callers that cannot provide scratch ---------------------------------------------------
+// Some hosts have nowhere to get device memory from at the point where they call an operator: a plugin
+// slot whose interface carries only the operator's tensors, a serving process that handed all device
+// memory to its own pool at start-up (a later driver allocation may fail, and it synchronises the whole
+// device), or a stateless hook that cannot keep a buffer between calls. For them the split-KV partials
+// live in an array that is part of the library image itself, so it exists on every device as soon as the
+// library is loaded and is never allocated or freed.
+constexpr size_t kStaticAttentionScratchBytes = size_t(EI_ATTENTION_STATIC_SCRATCH_BYTES);
+static __device__ __align__(256) unsigned char static_attention_scratch[kStaticAttentionScratchBytes];
+
+// Device address of the array on the current device; resolved on the first call per device.
+static void* static_attention_scratch_address() {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mutex;
+  static void* address[kMaxDevices] = {};
+  int device = 0;
+  EI_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) throw std::invalid_argument("Device ordinal is out of range");
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!address[device]) {
+    void* resolved = nullptr;
+    const cudaError_t status = cudaGetSymbolAddress(&resolved, static_attention_scratch);
+    if (status != cudaSuccess || !resolved)
+      throw std::runtime_error(std::string("Built-in attention scratch could not be resolved: ") +
+                               cudaGetErrorString(status));
+    address[device] = resolved;
+  }
+  return address[device];
+}
+
+ei_status ei_attention_prefill_static_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view3 v, ei_view3 out,
+                                           size_t offset) {
+  return guarded([&] {
+    const size_t length = offset + q.shape[0];
+    const size_t needed = attention_scratch_bytes(q.shape[0], q.shape[1], length);
+    if (needed > kStaticAttentionScratchBytes)
+      throw std::invalid_argument("Attention of " + std::to_string(q.shape[0]) + " rows x " +
+                                  std::to_string(q.shape[1]) + " heads over " + std::to_string(length) +
+                                  " positions needs " + std::to_string(needed) +
+                                  " bytes of split scratch, more than the " +
+                                  std::to_string(kStaticAttentionScratchBytes) +
+                                  " built into the library; call ei_attention_prefill_bf16 with caller-owned scratch");
+    // Nothing in the array has to start at zero: every partial the merge reads is written by this call.
+    run_attention(ctx, q, k, v, out, offset, nullptr, static_attention_scratch_address(),
+                  kStaticAttentionScratchBytes);
   });
 }
 

@@ -107,6 +107,17 @@ def attention_prefill(ctx, q, k, v, output, offset: int, scratch) -> None:
                                                abi.view3(output), offset, ptr, size))
 
 
+STATIC_ATTENTION_SCRATCH_BYTES = 10 * 1024 * 1024
+
+
+def attention_prefill_static(ctx, q, k, v, output, offset: int) -> None:
+    """attention_prefill with the split partials in the library's built-in array: allocates nothing, takes no
+    scratch; shapes needing more than STATIC_ATTENTION_SCRATCH_BYTES raise ValueError. Calls on one device
+    share the array and must not overlap."""
+    abi.check(_lib().ei_attention_prefill_static_bf16(C.byref(ctx), abi.view3(q), abi.view3(k), abi.view3(v),
+                                                      abi.view3(output), offset))
+
+
 def attention_verify(ctx, q, k_capacity, v_capacity, output, device_offset, scratch) -> None:
     ptr, size = _scratch(scratch)
     abi.check(_lib().ei_attention_verify_bf16(C.byref(ctx), abi.view3(q), abi.view3(k_capacity),

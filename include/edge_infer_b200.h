@@ -145,6 +145,24 @@ ei_status ei_attention_verify_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k
                                    ei_view3 v_capacity, ei_view3 out, const int32_t* device_offset,
                                    void* scratch, size_t scratch_bytes);
 
+/* No counterpart in the reference. ei_attention_prefill_bf16 for callers that cannot supply scratch: a
+ * plugin slot whose interface carries only the operator's tensors, a process that gave all device memory
+ * to its own pool at start-up, a stateless hook with nowhere to keep a buffer between calls. The split
+ * partials go to an array of EI_ATTENTION_STATIC_SCRATCH_BYTES that is part of the library image on every
+ * device; the call never allocates or frees device memory. Same arguments, validation and results as
+ * ei_attention_prefill_bf16 (bit-identical output). Limits and rules:
+ *  - shapes whose split partials exceed the array are rejected with EI_INVALID_ARGUMENT before any write
+ *    (the message states the bytes needed). The array holds 9 rows x 32 heads at any KV length; in
+ *    general 64 * rows * heads * 528 bytes suffice;
+ *  - the first call on each device resolves the array's address, with that device current; make that
+ *    call before starting any stream capture;
+ *  - every call on a device uses the same array, so two calls whose execution may overlap (different
+ *    streams or threads) race; keep them on one stream or serialise them. Nothing in the array needs
+ *    clearing between calls. */
+#define EI_ATTENTION_STATIC_SCRATCH_BYTES (10u * 1024u * 1024u)
+ei_status ei_attention_prefill_static_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view3 v,
+                                           ei_view3 out, size_t offset);
+
 /* ---- greedy sampling and acceptance -------------------------------------------------------------- */
 /* Bytes of scratch for ei_sample_greedy_bf16. */
 size_t ei_sample_scratch_bytes(size_t rows, size_t vocabulary);
