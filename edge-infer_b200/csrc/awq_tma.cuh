@@ -2,9 +2,10 @@
 //
 // A tile is 8 output features = 8 consecutive rows of the N-major packed weight matrix, over one K slice of
 // up to 4096 inputs. One thread brings a whole tile into shared memory with a single tiled TMA copy
-// (cp.async.bulk.tensor) that completes on an mbarrier, and with two more small copies for the tile's group
-// scales and packed zero points; a ring of tiles is always in flight per block, so HBM streams continuously,
-// independently of the warps' register scoreboards, and the loop issues no global loads at all.
+// (cp.async.bulk.tensor) that completes on an mbarrier; a ring of tiles is always in flight per block, so HBM
+// streams continuously, independently of the warps' register scoreboards, and the loop issues no global loads
+// at all. The group scales and packed zero points of all rows the block will touch come in up front, by one
+// box each (a TMA copy costs about 100 ns of the copy engine's time whatever its size, so few large copies).
 //
 // The weight matrix is described to TMA as a rank-3 tensor [unit of 256 inputs][row][128 bytes], so that the
 // staged tile is [unit][row][128 B] and the 128-byte swizzle places the 16-byte chunk j of row r at chunk
@@ -31,7 +32,7 @@
 
 namespace ei {
 
-constexpr int kAwqMaxStages = 10;
+constexpr int kAwqMaxStages = 12;
 constexpr int kAwqSliceUnits = 16;            // 256-input units per K slice: one per warp
 constexpr uint32_t kAwqWaitLimit = 1u << 22;  // polls of ~100 ns before a wait gives up
 
@@ -48,6 +49,8 @@ struct AwqLaunch {
   int tma_sz;           // 1: scales/zeros ride with the tile by TMA; 0: fetched up front by ordinary loads
   int scale_box;        // groups per staged scale row
   int zero_box;         // words per staged zero row
+  int sz_boxes;         // TMA boxes of scale / zero rows per block: 1, or 2 in pair mode (gate rows, up rows)
+  int sz_rows;          // rows per such box (<= 256)
 };
 
 __device__ __forceinline__ uint32_t smem_address(const void* p) {
@@ -94,11 +97,14 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       : "memory");
 }
 
+constexpr int kAwqPhaseTiles = 2;  // tiles a warp accumulates between two block-wide barriers
+constexpr int kAwqEarlyStages = 1; // tiles requested before the kernel waits for its predecessor
+
 struct AwqLayout {
   int weight_bytes;   // staged weight bytes of a tile: units_box KiB
-  int stage_bytes;    // weights + 1 KiB for the tile's scales (512 B) and zero points (128 B)
   int sz_tile_bytes;  // up-front mode: scales + zero nibbles of one tile, 16-byte padded
-  size_t part_offset, barrier_offset, sz_offset, stage_offset, total;
+  int sz_scale_bytes; // TMA mode: bytes of all staged scale rows (the zero-point rows follow)
+  size_t stage_offset, part_offset, barrier_offset, sz_offset, total;
 };
 
 // Offsets are relative to the first 1024-byte boundary of the dynamic shared memory (the swizzle needs it);
@@ -106,13 +112,15 @@ struct AwqLayout {
 __host__ __device__ inline AwqLayout awq_layout(const AwqLaunch& cfg) {
   AwqLayout l;
   l.weight_bytes = cfg.units_box * 1024;
-  l.stage_bytes = l.weight_bytes + 1024;
   l.sz_tile_bytes = cfg.tma_sz ? 0 : ((8 * cfg.units_box * 2 * 3) + 15) & ~15;
+  l.sz_scale_bytes = cfg.sz_boxes * cfg.sz_rows * cfg.scale_box * 2;
   l.stage_offset = 0;
-  l.part_offset = size_t(cfg.stages) * l.stage_bytes;
-  l.barrier_offset = l.part_offset + size_t(4) * kGemmWarps * 136 * sizeof(float);  // 2 buffers x 2 tiles
+  l.part_offset = size_t(cfg.stages) * l.weight_bytes;
+  l.barrier_offset = l.part_offset + size_t(2) * kAwqPhaseTiles * kGemmWarps * 136 * sizeof(float);
   l.sz_offset = l.barrier_offset + 128;
-  l.total = l.sz_offset + size_t(cfg.tiles_per_block) * l.sz_tile_bytes + 1024;
+  const size_t sz_bytes = cfg.tma_sz ? size_t(l.sz_scale_bytes) + size_t(cfg.sz_boxes) * cfg.sz_rows * cfg.zero_box * 4
+                                     : size_t(cfg.tiles_per_block) * l.sz_tile_bytes;
+  l.total = l.sz_offset + sz_bytes + 1024;
   return l;
 }
 
@@ -142,29 +150,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   unsigned char* stages = smem + layout.stage_offset;
   float* part = reinterpret_cast<float*>(smem + layout.part_offset);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + layout.barrier_offset);
+  uint64_t* sz_full = full + kAwqMaxStages;
   unsigned char* sz = smem + layout.sz_offset;
   const int scale_pitch = cfg.scale_box * 2, zero_pitch = cfg.zero_box * 4;
-  const uint32_t tile_bytes = uint32_t(layout.weight_bytes) + (cfg.tma_sz ? 8u * (scale_pitch + zero_pitch) : 0u);
 
-  // One thread brings in a whole tile.
+  // One thread brings in a whole tile with one copy.
   auto issue = [&](int index) {
     if (index >= item_count) return;
     const int stage = index % cfg.stages;
-    const int row = tile_of(item_begin + index) * 8;
-    unsigned char* dst = stages + size_t(stage) * layout.stage_bytes;
-    mbarrier_expect_tx(&full[stage], tile_bytes);
-    tma_load_3d(dst, &maps.weights, 0, row, unit_begin, &full[stage]);
-    if (cfg.tma_sz) {
-      tma_load_2d(dst + layout.weight_bytes, &maps.scales, unit_begin * 2, row, &full[stage]);
-      tma_load_2d(dst + layout.weight_bytes + 512, &maps.zeros, unit_begin / 4, row, &full[stage]);
-    }
+    mbarrier_expect_tx(&full[stage], uint32_t(layout.weight_bytes));
+    tma_load_3d(stages + size_t(stage) * layout.weight_bytes, &maps.weights, 0, tile_of(item_begin + index) * 8,
+                unit_begin, &full[stage]);
   };
   if (threadIdx.x == 0) {
     for (int s = 0; s < cfg.stages; ++s) mbarrier_init(&full[s], 1);
+    mbarrier_init(sz_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    for (int s = 0; s < cfg.stages; ++s) issue(s);
+    if (cfg.tma_sz) {
+      // Group scales and packed zero points of every row this block will touch: one box each (two in pair
+      // mode: the gate rows and the up rows). Rows past the matrix read as zero and are never used.
+      mbarrier_expect_tx(sz_full, uint32_t(cfg.sz_boxes * cfg.sz_rows * (scale_pitch + zero_pitch)));
+      for (int b = 0; b < cfg.sz_boxes; ++b) {
+        const int row = pair ? ((item_begin >> 1) + b * (tiles / 2)) * 8 : item_begin * 8;
+        tma_load_2d(sz + size_t(b) * cfg.sz_rows * scale_pitch, &maps.scales, unit_begin * 2, row, sz_full);
+        tma_load_2d(sz + layout.sz_scale_bytes + size_t(b) * cfg.sz_rows * zero_pitch, &maps.zeros, unit_begin / 4, row,
+                    sz_full);
+      }
+    }
+    // Only a few tiles now: requests made here are served before the activation loads below, and a full
+    // ring from every block would put those loads behind tens of megabytes of weight traffic.
+    for (int s = 0; s < kAwqEarlyStages && s < cfg.stages; ++s) issue(s);
   }
+
   if (!cfg.tma_sz) {
     // Scales (BF16) and zero nibbles (one byte each) of every tile of this block: [item][row][group].
     // Four elements per thread per round, all eight loads issued before the first store, so a round costs
@@ -210,13 +228,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const bool live = warp < units;
   CellFragments<kHigh> frag[8];
   {
-    const int k = (unit_begin + (live ? warp : 0)) * 256 + c * 64;
+    // Cell `cell` of lane (g, c) holds inputs [32 cell + 8 c, + 8) of the unit: the four lanes of a row read
+    // 64 contiguous bytes per load, so a warp-wide load touches 8 lines instead of 32.
+    const int k = (unit_begin + (live ? warp : 0)) * 256 + c * 8;
 #pragma unroll
     for (int cell = 0; cell < 8; ++cell)
-      load_cell<true, kHigh>(frag[cell], p.x, p.x_stride, live ? p.M : 0, g, k + cell * 8);
+      load_cell<true, kHigh>(frag[cell], p.x, p.x_stride, live ? p.M : 0, g, k + cell * 32);
   }
+  asm volatile("" ::: "memory");  // the activation loads are issued before the rest of the ring is requested
+  if (threadIdx.x == 0)
+    for (int s = kAwqEarlyStages; s < cfg.stages; ++s) issue(s);
   __syncthreads();  // barriers initialised; up-front scales / zeros visible
   grid_launch_dependents();
+  if (cfg.tma_sz && !mbarrier_wait(sz_full, 0)) {
+    if (p.status) atomicOr(p.status, 4);
+    return;  // the whole block sees the same incomplete phase
+  }
 
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
   const int e = warp * 8 + (lane & 7);
@@ -224,111 +251,131 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int rl = e >> 2, reg = e & 3;
   const int row = (rl >> 2) + (reg >= 2 ? 8 : 0);
   const int col = (rl & 3) * 2 + (reg & 1);
-  const int lane_group = warp * 2 + (c >> 1);  // this lane's scale group within the slice
-  // This lane's two 16-byte chunks of row g of unit `warp`, after the 128-byte swizzle.
-  const int chunk0 = warp * 1024 + g * 128 + (((2 * c) ^ g) << 4);
-  const int chunk1 = warp * 1024 + g * 128 + (((2 * c + 1) ^ g) << 4);
+  const int unit_group = warp * 2;  // the unit's two scale groups within the slice: cells 0-3 and cells 4-7
+  // Row g of unit `warp` in the staged tile; the lane's word of cell j is word c of 16-byte chunk (j ^ g).
+  const int row_offset = warp * 1024 + g * 128 + c * 4;
 
   // One tile: 8 words per lane, two accumulator chains so consecutive MMAs do not wait on each other.
   auto compute_tile = [&](int index, float (&acc)[4]) {
     float other[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
     if (!live) return;
-    const unsigned char* tile = stages + size_t(index % cfg.stages) * layout.stage_bytes;
-    uint32_t scale2, zero2;
+    const unsigned char* tile = stages + size_t(index % cfg.stages) * layout.weight_bytes;
+    uint32_t scale2[2], zero2[2];
     if (cfg.tma_sz) {
-      const unsigned char* tail = tile + layout.weight_bytes;
-      const uint32_t zero_word = *reinterpret_cast<const uint32_t*>(tail + 512 + g * zero_pitch + (lane_group >> 3) * 4);
-      scale2 = uint32_t(*reinterpret_cast<const unsigned short*>(tail + g * scale_pitch + lane_group * 2)) * 0x10001u;
-      zero2 = (0x4300u | ((zero_word >> ((lane_group & 7) * 4)) & 15u)) * 0x10001u;
+      const int sz_row = (pair ? (index & 1) * cfg.sz_rows + (index >> 1) * 8 : index * 8) + g;
+      const uint32_t zero_word =
+          *reinterpret_cast<const uint32_t*>(sz + layout.sz_scale_bytes + sz_row * zero_pitch + (unit_group >> 3) * 4);
+      const uint32_t scales = *reinterpret_cast<const uint32_t*>(sz + sz_row * scale_pitch + unit_group * 2);
+      scale2[0] = (scales & 0xffffu) * 0x10001u;
+      scale2[1] = (scales >> 16) * 0x10001u;
+      zero2[0] = (0x4300u | ((zero_word >> ((unit_group & 7) * 4)) & 15u)) * 0x10001u;
+      zero2[1] = (0x4300u | ((zero_word >> ((unit_group & 7) * 4 + 4)) & 15u)) * 0x10001u;
     } else {
       const int slice_groups = cfg.units_box * 2;
       const unsigned char* tile_sz = sz + size_t(index) * layout.sz_tile_bytes;
-      scale2 = uint32_t(reinterpret_cast<const unsigned short*>(tile_sz)[g * slice_groups + lane_group]) * 0x10001u;
-      zero2 = (0x4300u | tile_sz[8 * slice_groups * 2 + g * slice_groups + lane_group]) * 0x10001u;
+      const uint32_t scales = *reinterpret_cast<const uint32_t*>(tile_sz + (g * slice_groups + unit_group) * 2);
+      const unsigned char* nibbles = tile_sz + 8 * slice_groups * 2 + g * slice_groups + unit_group;
+      scale2[0] = (scales & 0xffffu) * 0x10001u;
+      scale2[1] = (scales >> 16) * 0x10001u;
+      zero2[0] = (0x4300u | nibbles[0]) * 0x10001u;
+      zero2[1] = (0x4300u | nibbles[1]) * 0x10001u;
     }
-    const uint4 w0 = *reinterpret_cast<const uint4*>(tile + chunk0);
-    const uint4 w1 = *reinterpret_cast<const uint4*>(tile + chunk1);
+    uint32_t words[8];
+#pragma unroll
+    for (int cell = 0; cell < 8; ++cell)
+      words[cell] = *reinterpret_cast<const uint32_t*>(tile + row_offset + (((cell ^ g) << 4)));
 #pragma unroll
     for (int cell = 0; cell < 8; ++cell) {
-      const uint4 wv = cell < 4 ? w0 : w1;
-      const int q = cell & 3;
-      const uint32_t word = q == 0 ? wv.x : q == 1 ? wv.y : q == 2 ? wv.z : wv.w;
-      const uint32_t b0 = dequant_pair(word, zero2, scale2);
-      const uint32_t b1 = dequant_pair(word >> 4, zero2, scale2);
-      const uint32_t b2 = dequant_pair(word >> 8, zero2, scale2);
-      const uint32_t b3 = dequant_pair(word >> 12, zero2, scale2);
+      const uint32_t word = words[cell], z = zero2[cell >> 2], sc = scale2[cell >> 2];
+      const uint32_t b0 = dequant_pair(word, z, sc);
+      const uint32_t b1 = dequant_pair(word >> 4, z, sc);
+      const uint32_t b2 = dequant_pair(word >> 8, z, sc);
+      const uint32_t b3 = dequant_pair(word >> 12, z, sc);
       mma_cell<kHigh>(acc, frag[cell], 0, b0, b1);
       mma_cell<kHigh>(other, frag[cell], 1, b2, b3);
     }
     acc[0] += other[0]; acc[1] += other[1]; acc[2] += other[2]; acc[3] += other[3];
   };
 
-  auto wait_tile = [&](int index) -> bool {
-    return mbarrier_wait(&full[index % cfg.stages], (index / cfg.stages) & 1);
+  // Reduction of one phase (kAwqPhaseTiles tiles): the partials were read into `loaded` right after the
+  // phase's barrier; the additions, the epilogue and the stores happen one tile of computation later, so the
+  // shared-memory latency is hidden behind that tile's arithmetic.
+  auto finish = [&](int index, const float (&loaded)[kAwqPhaseTiles][4]) {
+    float sums[kAwqPhaseTiles];
+#pragma unroll
+    for (int t = 0; t < kAwqPhaseTiles; ++t) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) sum += loaded[t][w];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      sums[t] = sum;
+    }
+    if (part_index != 0 || row >= p.M) return;
+    if (pair) {
+      // (index, index + 1) = (gate tile, up tile) of the same outputs.
+      const int out_n = tile_of(item_begin + index) * 8 + col;
+      float gate = sums[0], up = sums[1];
+      if (p.bias) {
+        gate += __bfloat162float(p.bias[out_n]);
+        up += __bfloat162float(p.bias[out_n + p.N / 2]);
+      }
+      p.out[size_t(row) * p.out_stride + out_n] =
+          __float2bfloat16_rn(silu_multiply_value(round_bf16(gate), round_bf16(up)));
+    } else {
+#pragma unroll
+      for (int t = 0; t < kAwqPhaseTiles; ++t) {
+        if (index + t >= item_count) break;
+        const int n = tile_of(item_begin + index + t) * 8 + col;
+        float sum = sums[t];
+        if (p.epilogue == kEpiPartial) {
+          p.partial[(size_t(slice) * p.M + row) * p.N + n] = sum;
+        } else {
+          if (p.bias) sum += __bfloat162float(p.bias[n]);
+          p.out[size_t(row) * p.out_stride + n] = __float2bfloat16_rn(sum);
+        }
+      }
+    }
   };
 
-  // Two tiles per block-wide barrier.
-  for (int index = 0; index < item_count; index += 2) {
-    const bool second = index + 1 < item_count;
-    float acc0[4], acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    bool ok = wait_tile(index);
-    if (ok) compute_tile(index, acc0);
-    if (ok && second) {
-      ok = wait_tile(index + 1);
-      if (ok) compute_tile(index + 1, acc1);
+  // kAwqPhaseTiles tiles per block-wide barrier; the partial buffers alternate between phases.
+  static_assert(kAwqPhaseTiles == 2, "the loop below is written for two tiles per phase");
+  float loaded[kAwqPhaseTiles][4];
+  int pending = -1;  // first item of the phase whose partials sit in `loaded`
+  for (int index = 0, phase = 0; index < item_count; index += kAwqPhaseTiles, phase ^= 1) {
+    float acc[kAwqPhaseTiles][4];
+    bool ok = mbarrier_wait(&full[index % cfg.stages], (index / cfg.stages) & 1);
+    if (ok) compute_tile(index, acc[0]);
+    if (ok && pending >= 0) finish(pending, loaded);
+    acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
+    if (ok && index + 1 < item_count) {
+      ok = mbarrier_wait(&full[(index + 1) % cfg.stages], ((index + 1) / cfg.stages) & 1);
+      if (ok) compute_tile(index + 1, acc[1]);
     }
     if (!ok) {
       if (p.status) atomicOr(p.status, 4);
       return;  // every thread of the block sees the same incomplete phase and leaves here
     }
-    float* mine = part + ((size_t((index >> 1) & 1) * 2) * kGemmWarps + warp) * kBlock;
-    *reinterpret_cast<float4*>(mine + lane * 4) = make_float4(acc0[0], acc0[1], acc0[2], acc0[3]);
-    *reinterpret_cast<float4*>(mine + kGemmWarps * kBlock + lane * 4) = make_float4(acc1[0], acc1[1], acc1[2], acc1[3]);
+    float* mine = part + (size_t(phase) * kAwqPhaseTiles * kGemmWarps + warp) * kBlock + lane * 4;
+#pragma unroll
+    for (int t = 0; t < kAwqPhaseTiles; ++t)
+      *reinterpret_cast<float4*>(mine + size_t(t) * kGemmWarps * kBlock) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
     __syncthreads();
-    // Every warp has finished reading these two stages: refill them with the tiles `stages` ahead.
+    // Every warp has finished reading these stages: refill them with the tiles `stages` ahead.
     if (threadIdx.x == 0) {
-      issue(index + cfg.stages);
-      issue(index + 1 + cfg.stages);
-    }
-    float sums[2];
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const float* src = part + ((size_t((index >> 1) & 1) * 2 + t) * kGemmWarps + part_index) * kBlock + e;
-      float sum = 0.0f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) sum += src[size_t(w) * 4 * kBlock];
-      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-      sums[t] = sum;
+      for (int t = 0; t < kAwqPhaseTiles; ++t) issue(index + t + cfg.stages);
     }
-    if (part_index == 0 && row < p.M) {
-      if (pair) {
-        // (index, index + 1) = (gate tile, up tile) of the same outputs.
-        const int out_n = tile_of(item_begin + index) * 8 + col;
-        float gate = sums[0], up = sums[1];
-        if (p.bias) {
-          gate += __bfloat162float(p.bias[out_n]);
-          up += __bfloat162float(p.bias[out_n + p.N / 2]);
-        }
-        p.out[size_t(row) * p.out_stride + out_n] =
-            __float2bfloat16_rn(silu_multiply_value(round_bf16(gate), round_bf16(up)));
-      } else {
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (t == 1 && !second) break;
-          const int n = tile_of(item_begin + index + t) * 8 + col;
-          float sum = sums[t];
-          if (p.epilogue == kEpiPartial) {
-            p.partial[(size_t(slice) * p.M + row) * p.N + n] = sum;
-          } else {
-            if (p.bias) sum += __bfloat162float(p.bias[n]);
-            p.out[size_t(row) * p.out_stride + n] = __float2bfloat16_rn(sum);
-          }
-        }
-      }
+    for (int t = 0; t < kAwqPhaseTiles; ++t) {
+      const float* src = part + ((size_t(phase) * kAwqPhaseTiles + t) * kGemmWarps + part_index) * kBlock + e;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) loaded[t][w] = src[size_t(w) * 4 * kBlock];
     }
+    pending = index;
   }
+  if (pending >= 0) finish(pending, loaded);
 }
 
 }  // namespace ei

@@ -355,6 +355,7 @@ void run_linear(ei_session& s, const PreparedLinear& w, const bf16* x, int rows,
   p.partial = s.partial;
   p.best_value = s.best_value;
   p.best_index = s.best_index;
+  p.status = &s.control->status;
   tick(s);
   launch_gemm(plan, w.quantized, p, s.stream, pdl);
   if (ksplit_out) *ksplit_out = plan.ksplit;

@@ -109,8 +109,8 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
   if (awq) {
     if (epilogue == kEpiArgmax) return plan;  // the vocabulary head is a dense matrix
     plan.tiles_per_block = ((chunks + groups - 1) / groups) * (pair ? 2 : 1);
-    // Feasible if two tiles fit in flight even when scales and zero points are staged up front.
-    AwqLaunch worst{plan.tiles_per_block, 2, std::min(kAwqSliceUnits, units_total), 0, 0, 0};
+    // Feasible if one phase of tiles fits in flight even when scales and zero points are staged up front.
+    AwqLaunch worst{plan.tiles_per_block, kAwqPhaseTiles, std::min(kAwqSliceUnits, units_total), 0, 0, 0, 0, 0};
     smem = awq_layout(worst).total;
     plan.smem_limit = smem_limit;
   }
@@ -160,12 +160,17 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
   AwqLaunch cfg{};
   cfg.tiles_per_block = plan.tiles_per_block;
   cfg.units_box = std::min(kAwqSliceUnits, units_total);
-  // TMA needs 16-byte aligned bases and row pitches.
-  cfg.tma_sz = aligned_16(p.scales) && aligned_16(p.zeros) && p.padded_groups % 8 == 0 && p.zero_stride % 4 == 0;
+  const bool pair = p.epilogue == kEpiSiluPair;
+  cfg.sz_boxes = pair ? 2 : 1;
+  cfg.sz_rows = plan.tiles_per_block / cfg.sz_boxes * 8;
+  // TMA needs 16-byte aligned bases and row pitches, and boxes of at most 256 rows.
+  cfg.tma_sz = aligned_16(p.scales) && aligned_16(p.zeros) && p.padded_groups % 8 == 0 && p.zero_stride % 4 == 0 &&
+               cfg.sz_rows <= 256;
   cfg.scale_box = cfg.tma_sz ? std::min(32, p.padded_groups) : 0;
   cfg.zero_box = cfg.tma_sz ? std::min(4, p.zero_stride) : 0;
+  if (!cfg.tma_sz) cfg.sz_boxes = cfg.sz_rows = 0;
   cfg.stages = kAwqMaxStages;
-  while (cfg.stages > 2 && awq_layout(cfg).total > plan.smem_limit) --cfg.stages;
+  while (cfg.stages > kAwqPhaseTiles && awq_layout(cfg).total > plan.smem_limit) --cfg.stages;
   const size_t smem = awq_layout(cfg).total;
   if (smem > plan.smem_limit) throw std::invalid_argument("small-M int4 GEMM does not fit in shared memory");
 
@@ -181,12 +186,12 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
   if (cfg.tma_sz) {
     const cuuint64_t scale_dims[2] = {cuuint64_t(p.padded_groups), cuuint64_t(p.N)};
     const cuuint64_t scale_strides[1] = {cuuint64_t(p.padded_groups) * 2};
-    const cuuint32_t scale_box[2] = {cuuint32_t(cfg.scale_box), 8};
+    const cuuint32_t scale_box[2] = {cuuint32_t(cfg.scale_box), cuuint32_t(cfg.sz_rows)};
     encode_map(&maps.scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, p.scales, scale_dims, scale_strides, scale_box,
                CU_TENSOR_MAP_SWIZZLE_NONE, "scales");
     const cuuint64_t zero_dims[2] = {cuuint64_t(p.zero_stride), cuuint64_t(p.N)};
     const cuuint64_t zero_strides[1] = {cuuint64_t(p.zero_stride) * 4};
-    const cuuint32_t zero_box[2] = {cuuint32_t(cfg.zero_box), 8};
+    const cuuint32_t zero_box[2] = {cuuint32_t(cfg.zero_box), cuuint32_t(cfg.sz_rows)};
     encode_map(&maps.zeros, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.zeros, zero_dims, zero_strides, zero_box,
                CU_TENSOR_MAP_SWIZZLE_NONE, "zero points");
   }

@@ -44,7 +44,10 @@ def test_awq_linear_sweep(cuda, package, oracle, ctx, rows, nk):
     out = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
     scratch = torch.empty(ops.linear_scratch_bytes(rows, k, n), dtype=torch.uint8, device="cuda")
     ops.awq_linear(ctx, dx, weight, out, scratch)
+    again = torch.empty_like(out)
+    ops.awq_linear(ctx, dx, weight, again, scratch)               # same bits on every call
     torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), again.view(torch.int16))
     # Oracle on a column subset (the CPU follows 256 columns in well under a second).
     cols = np.random.default_rng(n + k).choice(n, size=256, replace=False)
     dense = syn.awq_dequantize(q[cols], s[cols], z[cols], k)
@@ -107,6 +110,43 @@ def test_awq_bias_cancellation_known_answer(cuda, package, ctx, rows, kn):
     ops.awq_linear(ctx, to_dev(torch, syn.float_to_bf16(x)), weight, out, None)
     torch.cuda.synchronize()
     assert np.array_equal(syn.bf16_to_float(to_host(out)), np.tile(signs, (rows, 1)))
+
+
+@pytest.mark.parametrize("rows", [1, 9, 16])
+@pytest.mark.parametrize("fk", [(12288, 4096), (18944, 3584), (128, 512), (64, 4096)])
+def test_awq_gate_up_silu_matches_unfused_sequence(cuda, package, oracle, ctx, rows, fk):
+    """The fused SwiGLU projection against the reference's sequence (two projections, then silu_multiply:
+    runtime/include/execution/decoder.hpp:162-165): every rounding point is kept, so the bits agree with this
+    library's unfused operators up to the FP32 summation order, and with the oracle within the linear bound."""
+    torch, ops, syn = cuda, package.operators, package.synthetic
+    f, k = fk
+    q, s, z = syn.awq_triple(17, f"gateup{f}x{k}", 2 * f, k)
+    bias = syn.float_to_bf16(np.random.default_rng(3).standard_normal(2 * f, dtype=np.float32) * 0.05)
+    x = syn.float_to_bf16(np.random.default_rng(rows).standard_normal((rows, k), dtype=np.float32))
+    dq, ds, dz, db, dx = (torch.from_numpy(q).cuda(), to_dev(torch, s), torch.from_numpy(z).cuda(), to_dev(torch, bias),
+                          to_dev(torch, x))
+    weight = ops.prepare_awq(dq, ds, dz, 128, k, db)
+    scratch = torch.empty(ops.linear_scratch_bytes(rows, k, 2 * f), dtype=torch.uint8, device="cuda")
+    fused = torch.empty((rows, f), dtype=torch.bfloat16, device="cuda")
+    ops.awq_gate_up_silu(ctx, dx, weight, fused)
+    both = torch.empty((rows, 2 * f), dtype=torch.bfloat16, device="cuda")
+    ops.awq_linear(ctx, dx, weight, both, scratch)
+    unfused = torch.empty_like(fused)
+    gate, up = both[:, :f].contiguous(), both[:, f:].contiguous()
+    ops.silu_multiply(ctx, gate.view(-1), up.view(-1), unfused.view(-1))
+    torch.cuda.synchronize()
+    a, b = syn.bf16_to_float(to_host(fused)), syn.bf16_to_float(to_host(unfused))
+    assert np.array_equal(a, b)                                   # same kernel, same summation order
+    cols = np.random.default_rng(f).choice(f, size=min(f, 128), replace=False)
+    pick = np.concatenate([cols, cols + f])
+    dense = syn.awq_dequantize(q[pick], s[pick], z[pick], k)
+    ref = oracle.op_linear(syn.bf16_to_float(x), dense, syn.bf16_to_float(bias[pick]))
+    n = len(cols)
+    want = oracle.op_silu_multiply(ref[:, :n].reshape(-1), ref[:, n:].reshape(-1)).reshape(rows, n)
+    # A gate or up value that differs from the oracle's by one BF16 rounding moves the product by up to 2^-7
+    # of itself (times the slope of silu, < 1.1): allow that on top of the linear bound of each factor.
+    bound = 0.015625 + 0.03 * np.abs(want) + 0.02 * np.abs(ref[:, n:])
+    assert np.all(np.abs(a[:, cols] - want) <= bound)
 
 
 @pytest.mark.parametrize("rows", [1, 5, 16, 21])
