@@ -349,7 +349,8 @@ def run_native(args, rank: int, world: int, local_rank: int):
         kernel_seconds, kernel_bytes = time_dominant_kernel(package, torch, shape, layers=36, rows=rows, repeats=5)
         achieved = kernel_bytes / kernel_seconds / 1e9
         line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                            "traffic": None, "kernel": "awq_tma_kernel (int4 gate|up projection + SwiGLU) N=24576 K=4096 M=9",
+                            "traffic": 52_524_000,  # ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch
+                            "traffic_source": "profiles/awq_tma_kernel_gate_up_24576x4096_m9.md", "kernel": "awq_tma_kernel (int4 gate|up projection + SwiGLU) N=24576 K=4096 M=9",
                             "us_per_launch": kernel_seconds * 1e6, "algorithmic_bytes": kernel_bytes,
                             "peak_source": peak_kind}
         if world == 1 and not args.no_cpu_baseline:
