@@ -152,6 +152,10 @@ def cpu_verify_sample(oracle, package, threads: int, repeats: int):
     return step, sample, layer_times
 
 
+WORKLOAD = ("qwen3-8b-shape AWQ verify step: 36 layers, hidden 4096, 32Q/8KV, FFN 12288, vocab 151936, k=8 (9 rows), "
+            "prompt 2048, capacity 4096, p=0.2 draft substitution, one session per GPU")
+
+
 def run_reference(args, rank: int):
     if rank != 0:
         return
@@ -165,8 +169,8 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": step_seconds * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "qwen3-8b-shape AWQ verify step, k=8, prompt 2048, capacity 4096 (CPU, FP32 executor)",
-                   "expected_tokens_per_step": EXPECTED_EMITTED},
+        "config": {"workload": WORKLOAD, "sessions_per_gpu": 1, "executor": "CPU, FP32, AWQ weights dequantised",
+                   "tokens_per_step": EXPECTED_EMITTED},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -332,9 +336,7 @@ def run_native(args, rank: int, world: int, local_rank: int):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 activations, int4 group-128 weights, fp32 accumulation", "data": "synthetic",
-            "config": {"workload": "qwen3-8b-shape AWQ verify step: 36 layers, hidden 4096, 32Q/8KV, FFN 12288, vocab "
-                                   "151936, k=8 (9 rows), prompt 2048, capacity 4096, p=0.2 draft substitution, one "
-                                   "session per GPU",
+            "config": {"workload": WORKLOAD,
                        "sessions_per_gpu": 1, "l2_policy": "inputs larger than L2 (4.85 GB of weights per step)",
                        "tokens_per_step": totals[0] / (args.steps * world)},
             "clocks": clocks,
