@@ -112,6 +112,31 @@ def test_awq_bias_cancellation_known_answer(cuda, package, ctx, rows, kn):
     assert np.array_equal(syn.bf16_to_float(to_host(out)), np.tile(signs, (rows, 1)))
 
 
+@pytest.mark.parametrize("rows", [5, 16])
+@pytest.mark.parametrize("nk", [(4608, 3584), (3584, 18944), (512, 3584), (3584, 2048)])
+def test_awq_linear_qwen25_7b_shapes(cuda, package, oracle, ctx, rows, nk):
+    """Projections of the 28-head / 4-KV-head model with bias: 28 or 148 scale groups per row (row pitches TMA
+    cannot address), 14 and 74 units of 256 inputs (a short last slice), N not a multiple of the block count."""
+    torch, ops, syn = cuda, package.operators, package.synthetic
+    n, k = nk
+    q, s, z = syn.awq_triple(29, f"c5_{n}x{k}", n, k)
+    bias = syn.float_to_bf16(np.random.default_rng(n).standard_normal(n, dtype=np.float32) * 0.1)
+    x = syn.float_to_bf16(np.random.default_rng(rows + k).standard_normal((rows, k), dtype=np.float32))
+    dq, ds, dz, db, dx = (torch.from_numpy(q).cuda(), to_dev(torch, s), torch.from_numpy(z).cuda(), to_dev(torch, bias),
+                          to_dev(torch, x))
+    weight = ops.prepare_awq(dq, ds, dz, 128, k, db)
+    out = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(ops.linear_scratch_bytes(rows, k, n), dtype=torch.uint8, device="cuda")
+    ops.awq_linear(ctx, dx, weight, out, scratch)
+    torch.cuda.synchronize()
+    cols = np.random.default_rng(n + k).choice(n, size=256, replace=False)
+    dense = syn.awq_dequantize(q[cols], s[cols], z[cols], k)
+    ref = oracle.op_linear(syn.bf16_to_float(x), dense, syn.bf16_to_float(bias[cols]))
+    got = syn.bf16_to_float(to_host(out))[:, cols]
+    assert np.all(np.abs(got - ref) <= linear_tolerance(ref))
+    assert np.mean(got == ref) > 0.97
+
+
 @pytest.mark.parametrize("rows", [1, 9, 16])
 @pytest.mark.parametrize("fk", [(12288, 4096), (18944, 3584), (128, 512), (64, 4096)])
 def test_awq_gate_up_silu_matches_unfused_sequence(cuda, package, oracle, ctx, rows, fk):
