@@ -74,8 +74,22 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t* bar, uint32_t parity
       : "memory");
   return done != 0;
 }
-// Bounded wait; false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbarrier_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_address(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait; false if the phase did not complete within the limit. The non-blocking test comes first: a
+// try_wait with a time hint costs a few hundred cycles even when the phase has long completed, which is the
+// normal case here (the ring runs ahead of the arithmetic).
 __device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity) {
+  if (mbarrier_test_wait(bar, parity)) return true;
   for (uint32_t polls = 0; polls < kAwqWaitLimit; ++polls)
     if (mbarrier_try_wait(bar, parity)) return true;
   return false;
@@ -98,7 +112,7 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 }
 
 constexpr int kAwqPhaseTiles = 2;  // tiles a warp accumulates between two block-wide barriers
-constexpr int kAwqEarlyStages = 1; // tiles requested before the kernel waits for its predecessor
+constexpr int kAwqEarlyPhases = 1; // phases (pairs of tiles) requested before the kernel waits for its predecessor
 
 struct AwqLayout {
   int weight_bytes;   // staged weight bytes of a tile: units_box KiB
@@ -154,16 +168,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   unsigned char* sz = smem + layout.sz_offset;
   const int scale_pitch = cfg.scale_box * 2, zero_pitch = cfg.zero_box * 4;
 
-  // One thread brings in a whole tile with one copy.
-  auto issue = [&](int index) {
+  // One thread brings in the two tiles of a phase, one copy each, on one barrier (a wait costs a few hundred
+  // cycles even when the data has long arrived, so there is one per phase, not one per tile).
+  const int ring_phases = cfg.stages / kAwqPhaseTiles;
+  auto issue = [&](int phase) {
+    const int index = phase * kAwqPhaseTiles;
     if (index >= item_count) return;
-    const int stage = index % cfg.stages;
-    mbarrier_expect_tx(&full[stage], uint32_t(layout.weight_bytes));
-    tma_load_3d(stages + size_t(stage) * layout.weight_bytes, &maps.weights, 0, tile_of(item_begin + index) * 8,
-                unit_begin, &full[stage]);
+    const int slot = phase % ring_phases, tiles_here = min(kAwqPhaseTiles, item_count - index);
+    mbarrier_expect_tx(&full[slot], uint32_t(tiles_here * layout.weight_bytes));
+    for (int t = 0; t < tiles_here; ++t)
+      tma_load_3d(stages + size_t(slot * kAwqPhaseTiles + t) * layout.weight_bytes, &maps.weights, 0,
+                  tile_of(item_begin + index + t) * 8, unit_begin, &full[slot]);
   };
   if (threadIdx.x == 0) {
-    for (int s = 0; s < cfg.stages; ++s) mbarrier_init(&full[s], 1);
+    for (int s = 0; s < ring_phases; ++s) mbarrier_init(&full[s], 1);
     mbarrier_init(sz_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -180,7 +198,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     // Only a few tiles now: requests made here are served before the activation loads below, and a full
     // ring from every block would put those loads behind tens of megabytes of weight traffic.
-    for (int s = 0; s < kAwqEarlyStages && s < cfg.stages; ++s) issue(s);
+    for (int ph = 0; ph < kAwqEarlyPhases && ph < ring_phases; ++ph) issue(ph);
   }
 
   if (!cfg.tma_sz) {
@@ -237,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
   asm volatile("" ::: "memory");  // the activation loads are issued before the rest of the ring is requested
   if (threadIdx.x == 0)
-    for (int s = kAwqEarlyStages; s < cfg.stages; ++s) issue(s);
+    for (int ph = kAwqEarlyPhases; ph < ring_phases; ++ph) issue(ph);
   __syncthreads();  // barriers initialised; up-front scales / zeros visible
   grid_launch_dependents();
   if (cfg.tma_sz && !mbarrier_wait(sz_full, 0)) {
@@ -260,7 +278,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     float other[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
     if (!live) return;
-    const unsigned char* tile = stages + size_t(index % cfg.stages) * layout.weight_bytes;
+    const unsigned char* tile = stages + size_t(index % cfg.stages) * layout.weight_bytes;  // stages is even
     uint32_t scale2[2], zero2[2];
     if (cfg.tma_sz) {
       const int sz_row = (pair ? (index & 1) * cfg.sz_rows + (index >> 1) * 8 : index * 8) + g;
@@ -345,14 +363,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   int pending = -1;  // first item of the phase whose partials sit in `loaded`
   for (int index = 0, phase = 0; index < item_count; index += kAwqPhaseTiles, phase ^= 1) {
     float acc[kAwqPhaseTiles][4];
-    bool ok = mbarrier_wait(&full[index % cfg.stages], (index / cfg.stages) & 1);
+    const int step = index / kAwqPhaseTiles;
+    const bool ok = mbarrier_wait(&full[step % ring_phases], (step / ring_phases) & 1);
     if (ok) compute_tile(index, acc[0]);
     if (ok && pending >= 0) finish(pending, loaded);
     acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
-    if (ok && index + 1 < item_count) {
-      ok = mbarrier_wait(&full[(index + 1) % cfg.stages], ((index + 1) / cfg.stages) & 1);
-      if (ok) compute_tile(index + 1, acc[1]);
-    }
+    if (ok && index + 1 < item_count) compute_tile(index + 1, acc[1]);
     if (!ok) {
       if (p.status) atomicOr(p.status, 4);
       return;  // every thread of the block sees the same incomplete phase and leaves here
@@ -363,10 +379,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       *reinterpret_cast<float4*>(mine + size_t(t) * kGemmWarps * kBlock) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
     __syncthreads();
     // Every warp has finished reading these stages: refill them with the tiles `stages` ahead.
-    if (threadIdx.x == 0) {
-#pragma unroll
-      for (int t = 0; t < kAwqPhaseTiles; ++t) issue(index + t + cfg.stages);
-    }
+    if (threadIdx.x == 0) issue(step + ring_phases);
 #pragma unroll
     for (int t = 0; t < kAwqPhaseTiles; ++t) {
       const float* src = part + ((size_t(phase) * kAwqPhaseTiles + t) * kGemmWarps + part_index) * kBlock + e;

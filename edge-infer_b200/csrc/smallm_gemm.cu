@@ -170,7 +170,7 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
   cfg.zero_box = cfg.tma_sz ? std::min(4, p.zero_stride) : 0;
   if (!cfg.tma_sz) cfg.sz_boxes = cfg.sz_rows = 0;
   cfg.stages = kAwqMaxStages;
-  while (cfg.stages > kAwqPhaseTiles && awq_layout(cfg).total > plan.smem_limit) --cfg.stages;
+  while (cfg.stages > kAwqPhaseTiles && awq_layout(cfg).total > plan.smem_limit) cfg.stages -= kAwqPhaseTiles;
   const size_t smem = awq_layout(cfg).total;
   if (smem > plan.smem_limit) throw std::invalid_argument("small-M int4 GEMM does not fit in shared memory");
 
