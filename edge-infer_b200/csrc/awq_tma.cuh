@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int k = (unit_begin + (live ? warp : 0)) * 256 + c * 8;
 #pragma unroll
     for (int cell = 0; cell < 8; ++cell)
-      load_cell<true, kHigh>(frag[cell], p.x, p.x_stride, live ? p.M : 0, g, k + cell * 32);
+      load_cell<kHigh>(frag[cell], p.x, p.x_stride, live ? p.M : 0, g, k + cell * 32);
   }
   asm volatile("" ::: "memory");  // the activation loads are issued before the rest of the ring is requested
   if (threadIdx.x == 0)

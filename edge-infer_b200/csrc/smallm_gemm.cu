@@ -61,9 +61,9 @@ namespace {
 // Two buffers of per-warp FP32 partials: 16 warps x 136 floats each.
 constexpr size_t kPartBytes = size_t(2) * kGemmWarps * 136 * sizeof(float);
 
-template <bool kAwq, bool kHigh, int kUnits, int kDepth>
+template <bool kHigh, int kUnits, int kDepth>
 void launch_instance(const GemmPlan& plan, const GemmParams& params, cudaStream_t stream, bool pdl) {
-  auto kernel = smallm_gemm_kernel<kAwq, kHigh, kUnits, kDepth>;
+  auto kernel = smallm_gemm_kernel<kHigh, kUnits, kDepth>;
   static thread_local int configured_device = -1;
   int device = 0;
   EI_CUDA(cudaGetDevice(&device));
@@ -76,12 +76,12 @@ void launch_instance(const GemmPlan& plan, const GemmParams& params, cudaStream_
 }
 
 // Deeper prefetch where only the low eight rows hold fragments (half the pinned registers).
-template <bool kAwq, int kUnits, int kDepthHigh, int kDepthLow>
+template <int kUnits, int kDepthHigh, int kDepthLow>
 void launch_high(const GemmPlan& plan, const GemmParams& params, cudaStream_t stream, bool pdl) {
   if (plan.high)
-    launch_instance<kAwq, true, kUnits, kDepthHigh>(plan, params, stream, pdl);
+    launch_instance<true, kUnits, kDepthHigh>(plan, params, stream, pdl);
   else
-    launch_instance<kAwq, false, kUnits, kDepthLow>(plan, params, stream, pdl);
+    launch_instance<false, kUnits, kDepthLow>(plan, params, stream, pdl);
 }
 
 }  // namespace
@@ -215,9 +215,9 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
 void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
   if (awq) return launch_awq(plan, p, stream, pdl);
   const int U = plan.units_per_warp;
-  if (U == 1) return launch_high<false, 1, 6, 6>(plan, p, stream, pdl);
-  if (U == 2) return launch_high<false, 2, 4, 4>(plan, p, stream, pdl);
-  if (U == 4) return launch_high<false, 4, 2, 2>(plan, p, stream, pdl);
+  if (U == 1) return launch_high<1, 6, 6>(plan, p, stream, pdl);
+  if (U == 2) return launch_high<2, 4, 4>(plan, p, stream, pdl);
+  if (U == 4) return launch_high<4, 2, 2>(plan, p, stream, pdl);
   throw std::invalid_argument("small-M GEMM plan has no kernel instance");
 }
 

@@ -1,29 +1,27 @@
-// Small-M (<= 16 rows) weight-streaming GEMM for sm_100a: out[M,N] = x[M,K] * W[N,K]^T (+ bias).
+// Small-M (<= 16 rows) weight-streaming GEMMs for sm_100a: out[M,N] = x[M,K] * W[N,K]^T (+ bias).
 //
-// The path is HBM-bound on bytes and, for int4 weights, issue-bound on the nibble -> BF16 conversion, so
-// the inner loop is stripped to that conversion and the MMA:
-//  * every weight byte is read exactly once, straight from global memory into registers with 128-bit
-//    loads that bypass L1 (each quad of lanes reads 128 contiguous bytes of one weight row); the loads of
-//    the next kDepth items are kept in flight in registers while the current item is computed, and nothing
-//    is computed from a loaded word before its item is consumed (a dependent instruction would stall the
-//    in-order issue of the loads behind it);
-//  * the activations never change while a block runs and each of its 16 warps always works on the same
-//    slice of the input features (K is dealt to the warps in units of 256 inputs for int4, 64 for BF16), so
-//    a warp loads its A fragments once, already in the register order mma.sync wants, and keeps them in
-//    registers for the whole kernel: the loop has no shared-memory loads and no register shuffles;
-//  * weights are dequantised in registers and fed to mma.sync.m16n8k16 as the B operand. A shared-memory
-//    operand tensor-core path (tcgen05) would need the dequantised tile written to shared memory first;
-//    with <= 16 rows the tensor pipe is idle either way and the cost that matters is the conversion.
+// This header holds what the two kernels share (parameters, plan, epilogues, the exact int4 dequantisation,
+// the activation fragments) and the kernel for dense BF16 weights; the int4 kernel is in awq_tma.cuh.
 //
-// Work decomposition: persistent blocks of 16 warps. An item is one tile of 8 output features. Per item the
-// warps write their FP32 partial accumulators to shared memory and all 512 threads add them in a fixed order
-// (4 partials per thread, parts combined by shuffles), so results do not depend on scheduling. Input features beyond 16 units per block are split over blocks (ksplit) that
-// write FP32 partials to caller scratch for a separate fixed-order reduction.
+// Dense BF16 kernel (the vocabulary head and every projection of unquantised models). The path is HBM-bound:
+//  * every weight byte is read exactly once, straight from global memory into registers with 128-bit loads
+//    that bypass L1 (each quad of lanes reads 128 contiguous bytes of one weight row); the loads of the next
+//    kDepth items are kept in flight in registers while the current item is computed, and nothing is computed
+//    from a loaded word before its item is consumed (a dependent instruction would stall the in-order issue of
+//    the loads behind it);
+//  * the <= 16 activation rows are staged once per block in swizzled shared memory and read as A fragments;
+//    the weights are the B operand of mma.sync.m16n8k16 with FP32 accumulation.
 //
-// Rounding contract (reference operators/src/cuda/kernels/awq_gemv_gemm.cu:119-127, 318-329): int4 weights
-// are dequantised as round_bf16((w - z) * scale) - computed as an exact BF16 subtraction followed by one
-// correctly rounded BF16 multiply, which gives the same bits - products accumulate in FP32, the bias joins
-// the FP32 sum and the result is rounded once.
+// Work decomposition: persistent blocks of 16 warps. An item is one tile of 8 output features; K is dealt to
+// the warps in units of 64 inputs. Per item the warps write their FP32 partial accumulators to shared memory
+// and all 512 threads add them in a fixed order (4 partials per thread, parts combined by shuffles), so
+// results do not depend on scheduling. Input features beyond 64 units per block are split over blocks
+// (ksplit) that write FP32 partials to caller scratch for a separate fixed-order reduction.
+//
+// Rounding contract (reference operators/src/cuda/kernels/awq_gemv_gemm.cu:119-127, 318-329,
+// operators/src/cuda/execution.cu:299-324): int4 weights are dequantised as round_bf16((w - z) * scale) -
+// computed as an exact BF16 subtraction followed by one correctly rounded BF16 multiply, which gives the same
+// bits - products accumulate in FP32, the bias joins the FP32 sum and the result is rounded once.
 #pragma once
 
 #include "common.cuh"
@@ -95,9 +93,8 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, uint32_t zero
   return product;
 }
 
-// BF16 weights are bandwidth-bound, not issue-bound, and a warp covers up to four 64-input units, too many
-// fragments to pin in registers: there the activations sit in shared memory as 16-byte cells of 8 consecutive
-// inputs of one row. Cell (row r < 8, kb) lives at (kb * 8 + (r ^ swizzle(kb))) * 16, rows 8..15 in a second
+// With BF16 weights a warp covers up to four 64-input units, too many fragments to pin in registers: the
+// activations sit in shared memory as 16-byte cells of 8 consecutive inputs of one row. Cell (row r < 8, kb) lives at (kb * 8 + (r ^ swizzle(kb))) * 16, rows 8..15 in a second
 // array of the same shape; the swizzle uses the kb bits that differ between the four lanes of a quad so that
 // a quarter-warp's 128-bit loads fall into eight distinct bank groups.
 __device__ __forceinline__ int x_cell(int kb, int r) { return (kb * 8 + (r ^ (((kb >> 1) & 3) << 1))) * 16; }
@@ -118,38 +115,33 @@ __device__ __forceinline__ void stage_activations(const GemmParams& p, unsigned 
 }
 
 // Registers of one prefetched item (one tile) for one warp. Raw loaded words only.
-template <bool kAwq, int kUnits>
+template <int kUnits>
 struct ItemRegs {
   uint4 w[kUnits][2];
-  uint32_t scale[kAwq ? kUnits : 1];  // BF16 scale of the lane's group (low half)
-  uint32_t zero[kAwq ? kUnits : 1];   // packed zero word holding the lane's group
 };
 
-// A fragments of one 8-input cell: two MMAs' worth of (a0, a1, a2, a3). For int4 weights the 8 inputs are
+// A fragments of one 8-input cell of the int4 kernel: two MMAs' worth of (a0, a1, a2, a3). The 8 inputs are
 // taken in the order (0,4 | 1,5) and (2,6 | 3,7): the pair order the nibble extraction yields.
 template <bool kHigh>
 struct CellFragments {
   uint32_t a[2][kHigh ? 4 : 2];
 };
 
-template <bool kAwq, bool kHigh>
+// Loads the fragments of one cell for lane (g, c): 8 consecutive inputs of rows g and g + 8 starting at k.
+template <bool kHigh>
 __device__ __forceinline__ void load_cell(CellFragments<kHigh>& f, const bf16* x, int x_stride, int M, int g, int k) {
   uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
   if (g < M) lo = *reinterpret_cast<const uint4*>(x + size_t(g) * x_stride + k);
   if (kHigh && g + 8 < M) hi = *reinterpret_cast<const uint4*>(x + size_t(g + 8) * x_stride + k);
-  if (kAwq) {
-    // (k0k1, k2k3, k4k5, k6k7) -> (k0k4, k1k5, k2k6, k3k7)
-    uint4 t;
-    t.x = __byte_perm(lo.x, lo.z, 0x5410); t.y = __byte_perm(lo.x, lo.z, 0x7632);
-    t.z = __byte_perm(lo.y, lo.w, 0x5410); t.w = __byte_perm(lo.y, lo.w, 0x7632);
-    lo = t;
-    if (kHigh) {
-      t.x = __byte_perm(hi.x, hi.z, 0x5410); t.y = __byte_perm(hi.x, hi.z, 0x7632);
-      t.z = __byte_perm(hi.y, hi.w, 0x5410); t.w = __byte_perm(hi.y, hi.w, 0x7632);
-      hi = t;
-    }
-  }
+  // (k0k1, k2k3, k4k5, k6k7) -> (k0k4, k1k5, k2k6, k3k7)
+  uint4 t;
+  t.x = __byte_perm(lo.x, lo.z, 0x5410); t.y = __byte_perm(lo.x, lo.z, 0x7632);
+  t.z = __byte_perm(lo.y, lo.w, 0x5410); t.w = __byte_perm(lo.y, lo.w, 0x7632);
+  lo = t;
   if (kHigh) {
+    t.x = __byte_perm(hi.x, hi.z, 0x5410); t.y = __byte_perm(hi.x, hi.z, 0x7632);
+    t.z = __byte_perm(hi.y, hi.w, 0x5410); t.w = __byte_perm(hi.y, hi.w, 0x7632);
+    hi = t;
     f.a[0][0] = lo.x; f.a[0][1] = hi.x; f.a[0][2] = lo.y; f.a[0][3] = hi.y;
     f.a[1][0] = lo.z; f.a[1][1] = hi.z; f.a[1][2] = lo.w; f.a[1][3] = hi.w;
   } else {
@@ -167,10 +159,9 @@ __device__ __forceinline__ void mma_cell(float (&acc)[4], const CellFragments<kH
     mma_bf16_16816(acc, f.a[which][0], 0u, f.a[which][1], 0u, b0, b1);
 }
 
-template <bool kAwq, bool kHigh, int kUnits, int kDepth>
+template <bool kHigh, int kUnits, int kDepth>
 __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const GemmParams p) {
-  constexpr int kUnitK = kAwq ? 256 : 64;
-  constexpr int kCells = kAwq ? 8 : 2;  // 8-input cells a lane owns per unit
+  constexpr int kUnitK = 64;
   constexpr int kParts = 4;             // reduction parts per output: a warp's lanes are 4 parts x 8 elements
   constexpr int kBlock = 136;           // floats per warp in the partial buffer: 128 + 8 keeps loads conflict-free
   extern __shared__ __align__(16) unsigned char smem[];
@@ -193,29 +184,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
 
   // Per-lane bases of everything the lane ever loads for unit j; a tile only adds a row offset.
   const unsigned char* w_base[kUnits];
-  const unsigned short* s_base[kAwq ? kUnits : 1];
-  const int32_t* z_base[kAwq ? kUnits : 1];
-  int zero_shift[kAwq ? kUnits : 1];
   bool live[kUnits];
 #pragma unroll
   for (int j = 0; j < kUnits; ++j) {
     const int u = warp + kGemmWarps * j;
     live[j] = u < units;
     const int k = (unit_begin + (live[j] ? u : 0)) * kUnitK + c * (kUnitK / 4);
-    if (kAwq) {
-      w_base[j] = reinterpret_cast<const unsigned char*>(p.qweight + size_t(g) * (p.K / 8) + k / 8);
-      const int grp = k >> 7;
-      s_base[j] = reinterpret_cast<const unsigned short*>(p.scales) + size_t(g) * p.padded_groups + grp;
-      z_base[j] = p.zeros + size_t(g) * p.zero_stride + (grp >> 3);
-      zero_shift[j] = (grp & 7) * 4;
-    } else {
-      w_base[j] = reinterpret_cast<const unsigned char*>(p.w + size_t(g) * p.ldw + k);
-    }
+    w_base[j] = reinterpret_cast<const unsigned char*>(p.w + size_t(g) * p.ldw + k);
   }
-  const size_t w_tile_stride = kAwq ? size_t(8) * (p.K / 8) * 4 : size_t(8) * p.ldw * 2;  // bytes per tile
+  const size_t w_tile_stride = size_t(8) * p.ldw * 2;  // bytes per tile
 
-  ItemRegs<kAwq, kUnits> regs[kDepth];
-  auto prefetch = [&](ItemRegs<kAwq, kUnits>& r, int item) {
+  ItemRegs<kUnits> regs[kDepth];
+  auto prefetch = [&](ItemRegs<kUnits>& r, int item) {
     const bool valid = item < item_end;
     const int tile = valid ? tile_of(item) : 0;
 #pragma unroll
@@ -224,17 +204,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
         const unsigned char* src = w_base[j] + size_t(tile) * w_tile_stride;
         r.w[j][0] = ldg_stream(src);
         r.w[j][1] = ldg_stream(src + 16);
-        if (kAwq) {
-          r.scale[j] = __ldg(s_base[j] + size_t(tile) * 8 * p.padded_groups);
-          r.zero[j] = uint32_t(__ldg(z_base[j] + size_t(tile) * 8 * p.zero_stride));
-        }
       } else {
         r.w[j][0] = make_uint4(0, 0, 0, 0);
         r.w[j][1] = make_uint4(0, 0, 0, 0);
-        if (kAwq) {
-          r.scale[j] = 0;
-          r.zero[j] = 0;
-        }
       }
     }
   };
@@ -244,23 +216,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
   for (int s = 0; s < kDepth; ++s) prefetch(regs[s], item_begin + s);
   grid_dependency_wait();
 
-  // int4: fragments pinned in registers. BF16: activations staged in shared memory behind the partials.
-  CellFragments<kHigh> frag[kAwq ? kUnits : 1][kAwq ? kCells : 1];
+  // Activations staged in shared memory behind the partials.
   unsigned char* x_lo = smem + size_t(2) * kGemmWarps * kBlock * sizeof(float);
   unsigned char* x_hi = x_lo + size_t(units) * kUnitK * 16;
-  if (kAwq) {
-#pragma unroll
-    for (int j = 0; j < kUnits; ++j) {
-      const int u = warp + kGemmWarps * j;
-      const int k = (unit_begin + (live[j] ? u : 0)) * kUnitK + c * (kUnitK / 4);
-#pragma unroll
-      for (int cell = 0; cell < kCells; ++cell)
-        load_cell<kAwq, kHigh>(frag[j][cell], p.x, p.x_stride, live[j] ? p.M : 0, g, k + cell * 8);
-    }
-  } else {
-    stage_activations(p, x_lo, x_hi, kHigh, unit_begin * kUnitK, units * kUnitK);
-    __syncthreads();
-  }
+  stage_activations(p, x_lo, x_hi, kHigh, unit_begin * kUnitK, units * kUnitK);
+  __syncthreads();
   grid_launch_dependents();
 
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
@@ -281,26 +241,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
       float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int j = 0; j < kUnits; ++j) {
-        uint32_t scale2 = 0, zero2 = 0;
-        if (kAwq) {
-          scale2 = regs[s].scale[j] * 0x10001u;
-          zero2 = (0x4300u | ((regs[s].zero[j] >> zero_shift[j]) & 15u)) * 0x10001u;
-        }
 #pragma unroll
         for (int v = 0; v < 2; ++v) {
           const uint4 wv = regs[s].w[j][v];
-          if (kAwq) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t word = q == 0 ? wv.x : q == 1 ? wv.y : q == 2 ? wv.z : wv.w;
-              const uint32_t b0 = dequant_pair(word, zero2, scale2);
-              const uint32_t b1 = dequant_pair(word >> 4, zero2, scale2);
-              const uint32_t b2 = dequant_pair(word >> 8, zero2, scale2);
-              const uint32_t b3 = dequant_pair(word >> 12, zero2, scale2);
-              mma_cell<kHigh>(acc, frag[j][v * 4 + q], 0, b0, b1);
-              mma_cell<kHigh>(acc, frag[j][v * 4 + q], 1, b2, b3);
-            }
-          } else if (live[j]) {
+          if (live[j]) {
             // Cell of (unit, lane, v); both cells of a lane share the swizzle term.
             const int u = warp + kGemmWarps * j;
             const int cell = x_cell((u * kUnitK + c * (kUnitK / 4)) >> 3, g) + v * 128;
