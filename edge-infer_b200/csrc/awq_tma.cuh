@@ -270,39 +270,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int row = (rl >> 2) + (reg >= 2 ? 8 : 0);
   const int col = (rl & 3) * 2 + (reg & 1);
   const int unit_group = warp * 2;  // the unit's two scale groups within the slice: cells 0-3 and cells 4-7
-  // Row g of unit `warp` in the staged tile; the lane's word of cell j is word c of 16-byte chunk (j ^ g).
-  const int row_offset = warp * 1024 + g * 128 + c * 4;
+  // Everything a tile's addresses depend on is folded into per-lane constants here, so that the loop does no
+  // division and little integer arithmetic (the loop is issue-bound: every instruction in it counts).
+  // Row g of unit `warp` in a staged tile; the lane's word of cell j is word c of 16-byte chunk (j ^ g), and
+  // because bits 4-6 of this offset hold g, that word sits at (lane_word ^ (j << 4)).
+  const uint32_t stages_address = smem_address(stages);
+  const uint32_t lane_word = uint32_t(warp * 1024 + g * 128 + (g << 4) + c * 4);
+  // Scales / zero points of this lane's row and groups: TMA mode [box][row][group], up-front mode [item][...].
+  const uint32_t sz_address = smem_address(sz);
+  const uint32_t lane_scale = cfg.tma_sz ? sz_address + g * scale_pitch + unit_group * 2
+                                         : sz_address + (g * cfg.units_box * 2 + unit_group) * 2;
+  const uint32_t lane_zero = cfg.tma_sz ? sz_address + layout.sz_scale_bytes + g * zero_pitch + (unit_group >> 3) * 4
+                                        : sz_address + 8 * cfg.units_box * 2 * 2 + g * cfg.units_box * 2 + unit_group;
+  const int zero_shift = cfg.tma_sz ? (unit_group & 7) * 4 : 0;
+  // Row of tile t (0 or 1) of phase `step` in the staged scale / zero rows.
+  const int phase_rows = pair ? 8 : 16, second_rows = pair ? cfg.sz_rows : 8;
+
+  auto shared_u32 = [](uint32_t address) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
+    return v;
+  };
 
   // One tile: 8 words per lane, two accumulator chains so consecutive MMAs do not wait on each other.
-  auto compute_tile = [&](int index, float (&acc)[4]) {
+  // `tile_address`: the staged tile; `step`, `t`: phase and tile within the phase.
+  auto compute_tile = [&](uint32_t tile_address, int step, int t, float (&acc)[4]) {
     float other[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
     if (!live) return;
-    const unsigned char* tile = stages + size_t(index % cfg.stages) * layout.weight_bytes;  // stages is even
     uint32_t scale2[2], zero2[2];
     if (cfg.tma_sz) {
-      const int sz_row = (pair ? (index & 1) * cfg.sz_rows + (index >> 1) * 8 : index * 8) + g;
-      const uint32_t zero_word =
-          *reinterpret_cast<const uint32_t*>(sz + layout.sz_scale_bytes + sz_row * zero_pitch + (unit_group >> 3) * 4);
-      const uint32_t scales = *reinterpret_cast<const uint32_t*>(sz + sz_row * scale_pitch + unit_group * 2);
+      const int sz_row = step * phase_rows + t * second_rows;
+      const uint32_t zero_word = shared_u32(lane_zero + sz_row * zero_pitch);
+      const uint32_t scales = shared_u32(lane_scale + sz_row * scale_pitch);
       scale2[0] = (scales & 0xffffu) * 0x10001u;
       scale2[1] = (scales >> 16) * 0x10001u;
-      zero2[0] = (0x4300u | ((zero_word >> ((unit_group & 7) * 4)) & 15u)) * 0x10001u;
-      zero2[1] = (0x4300u | ((zero_word >> ((unit_group & 7) * 4 + 4)) & 15u)) * 0x10001u;
+      zero2[0] = (0x4300u | ((zero_word >> zero_shift) & 15u)) * 0x10001u;
+      zero2[1] = (0x4300u | ((zero_word >> (zero_shift + 4)) & 15u)) * 0x10001u;
     } else {
-      const int slice_groups = cfg.units_box * 2;
-      const unsigned char* tile_sz = sz + size_t(index) * layout.sz_tile_bytes;
-      const uint32_t scales = *reinterpret_cast<const uint32_t*>(tile_sz + (g * slice_groups + unit_group) * 2);
-      const unsigned char* nibbles = tile_sz + 8 * slice_groups * 2 + g * slice_groups + unit_group;
+      const uint32_t offset = uint32_t(step * kAwqPhaseTiles + t) * layout.sz_tile_bytes;
+      const uint32_t scales = shared_u32(lane_scale + offset);
+      uint32_t nibbles;
+      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(nibbles) : "r"(lane_zero + offset));
       scale2[0] = (scales & 0xffffu) * 0x10001u;
       scale2[1] = (scales >> 16) * 0x10001u;
-      zero2[0] = (0x4300u | nibbles[0]) * 0x10001u;
-      zero2[1] = (0x4300u | nibbles[1]) * 0x10001u;
+      zero2[0] = (0x4300u | (nibbles & 15u)) * 0x10001u;
+      zero2[1] = (0x4300u | ((nibbles >> 8) & 15u)) * 0x10001u;
     }
     uint32_t words[8];
 #pragma unroll
-    for (int cell = 0; cell < 8; ++cell)
-      words[cell] = *reinterpret_cast<const uint32_t*>(tile + row_offset + (((cell ^ g) << 4)));
+    for (int cell = 0; cell < 8; ++cell) words[cell] = shared_u32((tile_address + lane_word) ^ uint32_t(cell << 4));
 #pragma unroll
     for (int cell = 0; cell < 8; ++cell) {
       const uint32_t word = words[cell], z = zero2[cell >> 2], sc = scale2[cell >> 2];
@@ -361,14 +378,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   static_assert(kAwqPhaseTiles == 2, "the loop below is written for two tiles per phase");
   float loaded[kAwqPhaseTiles][4];
   int pending = -1;  // first item of the phase whose partials sit in `loaded`
-  for (int index = 0, phase = 0; index < item_count; index += kAwqPhaseTiles, phase ^= 1) {
+  int slot = 0;          // ring position of the current phase
+  uint32_t parity = 0;   // of the current pass over the ring
+  for (int index = 0, step = 0; index < item_count; index += kAwqPhaseTiles, ++step) {
+    const int phase = step & 1;
     float acc[kAwqPhaseTiles][4];
-    const int step = index / kAwqPhaseTiles;
-    const bool ok = mbarrier_wait(&full[step % ring_phases], (step / ring_phases) & 1);
-    if (ok) compute_tile(index, acc[0]);
+    const bool ok = mbarrier_wait(&full[slot], parity);
+    const uint32_t tile_address = stages_address + uint32_t(slot * kAwqPhaseTiles) * layout.weight_bytes;
+    if (ok) compute_tile(tile_address, step, 0, acc[0]);
     if (ok && pending >= 0) finish(pending, loaded);
     acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
-    if (ok && index + 1 < item_count) compute_tile(index + 1, acc[1]);
+    if (ok && index + 1 < item_count) compute_tile(tile_address + layout.weight_bytes, step, 1, acc[1]);
+    if (++slot == ring_phases) {
+      slot = 0;
+      parity ^= 1;
+    }
     if (!ok) {
       if (p.status) atomicOr(p.status, 4);
       return;  // every thread of the block sees the same incomplete phase and leaves here
@@ -379,7 +403,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       *reinterpret_cast<float4*>(mine + size_t(t) * kGemmWarps * kBlock) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
     __syncthreads();
     // Every warp has finished reading these stages: refill them with the tiles `stages` ahead.
-    if (threadIdx.x == 0) issue(step + ring_phases);
+    if (threadIdx.x == 0) issue(step + ring_phases);  // lands in the slot this phase has just left
 #pragma unroll
     for (int t = 0; t < kAwqPhaseTiles; ++t) {
       const float* src = part + ((size_t(phase) * kAwqPhaseTiles + t) * kGemmWarps + part_index) * kBlock + e;
