@@ -334,24 +334,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   };
 
   // Reduction of one phase (kAwqPhaseTiles tiles): the partials were read into `loaded` right after the
-  // phase's barrier; the additions, the epilogue and the stores happen one tile of computation later, so the
-  // shared-memory latency is hidden behind that tile's arithmetic.
-  auto finish = [&](int index, const float (&loaded)[kAwqPhaseTiles][4]) {
-    float sums[kAwqPhaseTiles];
-#pragma unroll
-    for (int t = 0; t < kAwqPhaseTiles; ++t) {
-      float sum = 0.0f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) sum += loaded[t][w];
-      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-      sums[t] = sum;
-    }
-    if (part_index != 0 || row >= p.M) return;
+  // phase's barrier; the additions happen one tile of computation later, so the shared-memory latency is
+  // hidden behind that tile's arithmetic. After the shuffles all four parts of a warp hold the same sums:
+  // part q keeps those of phases q, q + 4, q + 8, ... and the epilogue runs once every four phases with all 32
+  // lanes busy instead of every phase with 8 (this loop is issue-bound: the epilogue's instructions count).
+  float held[kAwqPhaseTiles] = {0.0f, 0.0f};
+  auto emit = [&](int first_step, int last_step) {  // epilogue of phases first_step + part_index <= last_step
+    const int step = first_step + part_index;
+    if (step > last_step || row >= p.M) return;
+    const int index = step * kAwqPhaseTiles;
     if (pair) {
       // (index, index + 1) = (gate tile, up tile) of the same outputs.
       const int out_n = tile_of(item_begin + index) * 8 + col;
-      float gate = sums[0], up = sums[1];
+      float gate = held[0], up = held[1];
       if (p.bias) {
         gate += __bfloat162float(p.bias[out_n]);
         up += __bfloat162float(p.bias[out_n + p.N / 2]);
@@ -363,7 +358,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int t = 0; t < kAwqPhaseTiles; ++t) {
         if (index + t >= item_count) break;
         const int n = tile_of(item_begin + index + t) * 8 + col;
-        float sum = sums[t];
+        float sum = held[t];
         if (p.epilogue == kEpiPartial) {
           p.partial[(size_t(slice) * p.M + row) * p.N + n] = sum;
         } else {
@@ -373,11 +368,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
   };
+  auto finish = [&](int step, const float (&loaded)[kAwqPhaseTiles][4]) {
+#pragma unroll
+    for (int t = 0; t < kAwqPhaseTiles; ++t) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) sum += loaded[t][w];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      if (part_index == (step & 3)) held[t] = sum;
+    }
+    if ((step & 3) == 3) emit(step - 3, step);
+  };
 
   // kAwqPhaseTiles tiles per block-wide barrier; the partial buffers alternate between phases.
   static_assert(kAwqPhaseTiles == 2, "the loop below is written for two tiles per phase");
   float loaded[kAwqPhaseTiles][4];
-  int pending = -1;  // first item of the phase whose partials sit in `loaded`
+  int pending = -1;  // phase whose partials sit in `loaded`
   int slot = 0;          // ring position of the current phase
   uint32_t parity = 0;   // of the current pass over the ring
   for (int index = 0, step = 0; index < item_count; index += kAwqPhaseTiles, ++step) {
@@ -410,9 +417,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
       for (int w = 0; w < 4; ++w) loaded[t][w] = src[size_t(w) * 4 * kBlock];
     }
-    pending = index;
+    pending = step;
   }
-  if (pending >= 0) finish(pending, loaded);
+  if (pending >= 0) {
+    finish(pending, loaded);
+    if ((pending & 3) != 3) emit(pending & ~3, pending);
+  }
 }
 
 }  // namespace ei
