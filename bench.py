@@ -305,8 +305,12 @@ def run_native(args, rank: int, world: int, local_rank: int):
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     sampler.start()
+    if args.profile_region:
+        torch.cuda.profiler.start()                    # for `ncu --profile-from-start off`: the timed steps only
     emitted, elapsed_ms, mean_context = device_loop(args.steps)
     torch.cuda.synchronize()
+    if args.profile_region:
+        torch.cuda.profiler.stop()
     if dist:
         dist.barrier()
     clocks = sampler.stop()
@@ -374,6 +378,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--profile-region", action="store_true",
+                        help="bracket the timed steps with cudaProfilerStart/Stop (for a profiler started with "
+                             "profiling off); the numbers of such a run are not bench values")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
