@@ -233,6 +233,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
   int best_index = 0x7fffffff;
   float gate_sum = 0.0f;  // fused SwiGLU: the gate tile's sum waits here for the up tile
 
+  const bool high_row = g + 8 < p.M;  // this lane's second fragment row exists (9 rows: only one lane group)
   for (int base = item_begin; base < item_end; base += kDepth) {
 #pragma unroll
     for (int s = 0; s < kDepth; ++s) {
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
             const int cell = x_cell((u * kUnitK + c * (kUnitK / 4)) >> 3, g) + v * 128;
             const uint4 xa = *reinterpret_cast<const uint4*>(x_lo + cell);
             uint4 xb = make_uint4(0, 0, 0, 0);
-            if (kHigh) xb = *reinterpret_cast<const uint4*>(x_hi + cell);
+            if (kHigh && high_row) xb = *reinterpret_cast<const uint4*>(x_hi + cell);  // rows >= M are zero
             mma_bf16_16816(acc, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
             mma_bf16_16816(acc, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
           }
