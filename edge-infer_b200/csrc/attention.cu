@@ -61,8 +61,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
 }
 
 __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
+  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   extern __shared__ __align__(128) unsigned char smem[];
-  grid_dependency_wait();
+  // The context length was written by the previous step; the preceding kernel of this step only appends the
+  // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
   const int offset = p.device_offset ? *p.device_offset : p.host_offset;
   const int length = offset + p.rows;
   const int split = blockIdx.x, kv_head = blockIdx.y;
@@ -78,8 +80,11 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   const bf16* k_base = p.k + size_t(kv_head) * kDim;
   const bf16* v_base = p.v + size_t(kv_head) * kDim;
 
+  const bool settled = end <= offset;  // no row of this chunk is written by the preceding kernel
+  if (!settled) grid_dependency_wait();
   load_tile(k_smem[0], v_smem[0], k_base, v_base, p.kv_stride, start, end);
   cp_async_commit();
+  if (settled) grid_dependency_wait();  // the queries come from the preceding kernel
 
   // Stacked row i = r * group + hq  ->  query row r, query head kv_head * group + hq.
   const int i_lo = warp * 16 + g, i_hi = i_lo + 8;
@@ -195,7 +200,6 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
     }
     __syncthreads();  // the buffer is refilled two iterations from now
   }
-  grid_launch_dependents();
 
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -228,6 +232,7 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
 // splits w, w+4, ... and the four partial sums are added in warp order. The order of every addition is
 // fixed, so replays give identical bits.
 __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionParams p) {
+  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float weights[64];
   __shared__ float warp_values[4];
   __shared__ float4 partial_out[4][32];
@@ -266,7 +271,6 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   }
   partial_out[warp][lane] = accumulator;
   __syncthreads();
-  grid_launch_dependents();
   if (warp != 0) return;
   denominator = (warp_values[0] + warp_values[1]) + (warp_values[2] + warp_values[3]);
   const float4 a = partial_out[0][lane], b = partial_out[1][lane], c = partial_out[2][lane], d = partial_out[3][lane];
