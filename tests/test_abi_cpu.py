@@ -70,3 +70,47 @@ def test_synthetic_awq_packing_roundtrip(package):
     w = (q.view(np.uint32)[3, k // 8] >> ((k % 8) * 4)) & 15
     zero = (z.view(np.uint32)[3, 0] >> 4) & 15
     assert dense[3, k] == (np.float32(w) - np.float32(zero)) * syn.bf16_to_float(s[3:4, 1:2])[0, 0]
+
+
+SHIM_PROGRAM = r"""
+#include <cstdio>
+#include "edge_infer_b200.hpp"
+using namespace edge_infer_b200;
+int main() {
+  // Argument validation happens before any CUDA call, so these paths run without a GPU: a null weight must
+  // surface as std::invalid_argument, the exception the reference's operator throws for the same mistake.
+  op::cuda::ExecutionContext ctx{};
+  TensorView<const std::uint16_t, 2> x{};
+  TensorView<std::uint16_t, 2> y{};
+  op::cuda::AwqLinearWeight<std::uint16_t> weight{};
+  int caught = 0;
+  try {
+    op::cuda::awq_linear<std::uint16_t>(ctx, x, weight, y);
+  } catch (const std::invalid_argument&) {
+    caught = 1;
+  } catch (const std::exception&) {
+    caught = 2;
+  }
+  std::printf("%d %s\n", caught, ei_version());
+  return caught == 1 ? 0 : 1;
+}
+"""
+
+
+def test_cpp_shim_compiles_links_and_maps_errors(package, tmp_path):
+    """include/edge_infer_b200.hpp: the op::cuda names over the C ABI, exceptions as in the reference."""
+    import shutil
+    import subprocess
+
+    if shutil.which("g++") is None:
+        import pytest
+        pytest.skip("no g++")
+    library = Path(package.abi.LIB_PATH)
+    source = tmp_path / "shim.cpp"
+    source.write_text(SHIM_PROGRAM)
+    binary = tmp_path / "shim"
+    subprocess.run(["g++", "-std=c++17", "-I", str(ROOT / "include"), str(source), "-o", str(binary),
+                    f"-L{library.parent}", "-ledge_infer_b200", f"-Wl,-rpath,{library.parent}"], check=True)
+    result = subprocess.run([str(binary)], capture_output=True, text=True)
+    assert result.returncode == 0, result.stdout + result.stderr
+    assert result.stdout.startswith("1 ")
