@@ -128,6 +128,9 @@ PROTOTYPES = {
     "ei_session_prefill": (_S, [_P, _P, _Z, C.POINTER(_P), _P]),
     "ei_session_decode": (_S, [_P, C.c_uint32, C.POINTER(_P)]),
     "ei_session_verify": (_S, [_P, _P, _Z, C.POINTER(VerifyResult), C.POINTER(_P)]),
+    "ei_batch_create": (_S, [C.POINTER(_P), _Z, C.POINTER(_P)]),
+    "ei_batch_destroy": (None, [_P]),
+    "ei_batch_verify": (_S, [_P, _P, _Z, C.POINTER(VerifyResult)]),
     "ei_session_verify_enqueue": (_S, [_P, _P, _Z, _Z, _Z]),
     "ei_session_drain": (_S, [_P, C.POINTER(VerifyResult), C.POINTER(C.c_uint64)]),
     "ei_session_truncate": (_S, [_P, _Z]),

@@ -283,6 +283,14 @@ struct ei_session {
   cudaGraphExec_t graphs[3][kMaxRows + 1] = {};
 };
 
+// A fixed set of sessions of one model that are verified together: their rows are stacked into one
+// [sessions * rows, hidden] forward, so every weight is streamed once for all of them; attention, KV append
+// and acceptance stay per session. The first session lends its workspace and stream.
+struct ei_batch {
+  std::vector<ei_session*> sessions;
+  cudaGraphExec_t graphs[kMaxRows + 1] = {};  // by rows per session
+};
+
 namespace {
 
 enum StepKind { kVerifyHost = 0, kVerifyDevice = 1, kCommitAllWithHead = 2, kCommitAllNoHead = 3 };
@@ -560,6 +568,145 @@ void submit_step(ei_session& s, int rows, StepKind kind) {
   EI_CUDA(cudaGraphLaunch(exec, s.stream));
 }
 
+// One verify step of every session of the batch, `rows` tokens each, on the leader's stream and workspace.
+void enqueue_batch_step(ei_batch& batch, int rows) {
+  ei_session& lead = *batch.sessions[0];
+  const ei_model& m = *lead.model;
+  const auto& c = m.config;
+  const int count = int(batch.sessions.size()), total = count * rows;
+  const int heads = int(c.n_heads), kv_heads = int(c.n_kv_heads), hidden = int(c.hidden_size), ffn = int(c.intermediate_size);
+  const int qkv_width = (heads + 2 * kv_heads) * 128, kv_width = kv_heads * 128;
+  const bool pdl = true;
+
+  for (int j = 0; j < count; ++j) {
+    ei_session& s = *batch.sessions[j];
+    EmbedParams e{};
+    e.tokens = lead.tokens + j * rows;
+    e.control = s.control;
+    e.step_tokens = lead.step_tokens + j * rows;
+    e.table = m.embedding;
+    e.vocab = int(c.vocab_size);
+    e.hidden = hidden;
+    e.rows = rows;
+    e.capacity = int(s.capacity);
+    e.norm_weight = m.layers[0].attention_norm;
+    e.eps = c.rms_norm_eps;
+    e.residual = lead.residual + size_t(j) * rows * hidden;
+    e.normed = lead.normed + size_t(j) * rows * hidden;
+    tick(lead);
+    launch_embed_norm(e, lead.stream, false);
+  }
+  const size_t scratch_floats = attention_scratch_bytes(rows, heads, lead.capacity) / sizeof(float);
+  for (size_t layer = 0; layer < m.layers.size(); ++layer) {
+    const auto& L = m.layers[layer];
+    if (has_plan(lead, L.qkv, total, kEpiStore))
+      run_linear(lead, L.qkv, lead.normed, total, kEpiStore, lead.qkv, qkv_width, pdl);
+    else
+      run_generic(lead, L.qkv, lead.normed, total, lead.qkv, pdl);
+    for (int j = 0; j < count; ++j) {
+      ei_session& s = *batch.sessions[j];
+      QkvParams q{};
+      q.qkv = lead.qkv + size_t(j) * rows * qkv_width;
+      q.rows = rows;
+      q.heads = heads;
+      q.kv_heads = kv_heads;
+      q.qkv_stride = qkv_width;
+      q.q_norm = c.qk_norm ? L.q_norm : nullptr;
+      q.k_norm = c.qk_norm ? L.k_norm : nullptr;
+      q.eps = c.rms_norm_eps;
+      q.rope_table = m.rope_table;
+      q.max_positions = int(c.max_position_embeddings);
+      q.control = s.control;
+      q.capacity = int(s.capacity);
+      q.k_cache = s.k_cache + layer * s.capacity * kv_width;
+      q.v_cache = s.v_cache + layer * s.capacity * kv_width;
+      tick(lead);
+      launch_qk_norm_rope_store(q, lead.stream, pdl);
+    }
+    for (int j = 0; j < count; ++j) {
+      ei_session& s = *batch.sessions[j];
+      AttentionParams a{};
+      a.q = lead.qkv + size_t(j) * rows * qkv_width;
+      a.q_stride = qkv_width;
+      a.k = s.k_cache + layer * s.capacity * kv_width;
+      a.v = s.v_cache + layer * s.capacity * kv_width;
+      a.kv_stride = kv_width;
+      a.rows = rows;
+      a.heads = heads;
+      a.kv_heads = kv_heads;
+      a.capacity = int(s.capacity);
+      a.device_offset = &s.control->context;
+      a.chunk = s.attention_chunk;
+      a.max_splits = s.attention_splits;
+      a.scratch = lead.attention_scratch + size_t(j) * scratch_floats;
+      a.out = lead.attention + size_t(j) * rows * heads * 128;
+      a.out_stride = heads * 128;
+      tick(lead);
+      tick(lead);
+      launch_verify_attention(a, lead.stream, pdl);
+    }
+    run_projection_residual_norm(lead, L.o, lead.attention, total, L.ffn_norm, pdl);
+    if (has_plan(lead, L.gate_up, total, kEpiSiluPair)) {
+      run_linear(lead, L.gate_up, lead.normed, total, kEpiSiluPair, lead.act, ffn, pdl);
+    } else {
+      if (has_plan(lead, L.gate_up, total, kEpiStore))
+        run_linear(lead, L.gate_up, lead.normed, total, kEpiStore, lead.gate_up, 2 * ffn, pdl);
+      else
+        run_generic(lead, L.gate_up, lead.normed, total, lead.gate_up, pdl);
+      tick(lead);
+      launch(silu_pair_rows_kernel, dim3(std::min(1024, (total * ffn + 255) / 256)), dim3(256), 0, lead.stream, pdl,
+             (const bf16*)lead.gate_up, total, ffn, lead.act);
+    }
+    const bf16* next_norm = layer + 1 < m.layers.size() ? m.layers[layer + 1].attention_norm : m.output_norm;
+    run_projection_residual_norm(lead, L.down, lead.act, total, next_norm, pdl);
+  }
+  int parts = 0;
+  if (has_plan(lead, m.lm_head, total, kEpiArgmax)) {
+    run_linear(lead, m.lm_head, lead.normed, total, kEpiArgmax, lead.logits, int(c.vocab_size), pdl, &parts);
+  } else {
+    run_generic(lead, m.lm_head, lead.normed, total, lead.logits, pdl);
+    parts = std::min(148, sample_partial_blocks(c.vocab_size, m.multiprocessors));
+    tick(lead);
+    launch_argmax_partials(lead.logits, total, c.vocab_size, c.vocab_size, lead.best_value, lead.best_index, parts,
+                           lead.stream, pdl);
+  }
+  // Greedy token, acceptance and commit per session, on its own rows of the per-block partials.
+  for (int j = 0; j < count; ++j) {
+    ei_session& s = *batch.sessions[j];
+    tick(lead);
+    launch_finalize(lead.best_value + j * rows, lead.best_index + j * rows, parts, rows, lead.targets + j * rows,
+                    lead.step_tokens + j * rows, s.control, nullptr, nullptr, nullptr, lead.stream, pdl);
+  }
+}
+
+void submit_batch_step(ei_batch& batch, int rows) {
+  ei_session& lead = *batch.sessions[0];
+  if (!lead.use_graph) {
+    enqueue_batch_step(batch, rows);
+    return;
+  }
+  cudaGraphExec_t& exec = batch.graphs[rows];
+  if (!exec) {
+    enqueue_batch_step(batch, rows);  // warm run: real work, kernel attributes, first-use set-up
+    cudaGraph_t graph = nullptr;
+    EI_CUDA(cudaStreamBeginCapture(lead.stream, cudaStreamCaptureModeThreadLocal));
+    try {
+      enqueue_batch_step(batch, rows);
+    } catch (...) {
+      cudaStreamEndCapture(lead.stream, &graph);
+      if (graph) cudaGraphDestroy(graph);
+      throw;
+    }
+    EI_CUDA(cudaStreamEndCapture(lead.stream, &graph));
+    const cudaError_t status = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    EI_CUDA(status);
+    return;  // the warm run already executed this step
+  }
+  tick(lead);
+  EI_CUDA(cudaGraphLaunch(exec, lead.stream));
+}
+
 void read_control(ei_session& s) {
   EI_CUDA(cudaMemcpyAsync(s.host_control, s.control, sizeof(Control), cudaMemcpyDeviceToHost, s.stream));
   synchronize(s);
@@ -574,6 +721,7 @@ void check_status(ei_session& s) {
     EI_CUDA(cudaMemcpyAsync(&s.control->status, &zero, sizeof(int), cudaMemcpyHostToDevice, s.stream));
     synchronize(s);
     if (status & 2) throw std::invalid_argument("Session token id exceeds vocabulary");
+    if (status & 4) throw std::runtime_error("A bounded wait inside a kernel gave up");
     throw LengthError("Session context capacity exhausted");
   }
 }
@@ -871,6 +1019,74 @@ ei_status ei_session_verify(ei_session* session, const uint32_t* host_tokens, si
     }
     *result = s.host_control->last;
     if (logits) *logits = s.logits;
+  });
+}
+
+ei_status ei_batch_create(ei_session* const* sessions, size_t count, ei_batch** out) {
+  return guarded([&] {
+    if (!sessions || !count || count > kMaxRows || !out) throw std::invalid_argument("A batch takes 1..16 sessions");
+    auto batch = std::make_unique<ei_batch>();
+    for (size_t j = 0; j < count; ++j) {
+      ei_session* s = sessions[j];
+      if (!s) throw std::invalid_argument("session is null");
+      if (s->model != sessions[0]->model) throw std::invalid_argument("Batched sessions must share one model");
+      if (s->capacity != sessions[0]->capacity)
+        throw std::invalid_argument("Batched sessions must have the same context capacity");
+      for (size_t i = 0; i < j; ++i)
+        if (sessions[i] == s) throw std::invalid_argument("A session appears twice in the batch");
+      batch->sessions.push_back(s);
+    }
+    *out = batch.release();
+  });
+}
+
+void ei_batch_destroy(ei_batch* batch) {
+  if (!batch) return;
+  for (auto& exec : batch->graphs)
+    if (exec) cudaGraphExecDestroy(exec);
+  delete batch;
+}
+
+ei_status ei_batch_verify(ei_batch* batch, const uint32_t* host_tokens, size_t rows, ei_verify_result* results) {
+  return guarded([&] {
+    if (!batch) throw std::invalid_argument("batch is null");
+    const size_t count = batch->sessions.size();
+    if (!host_tokens || !results || !rows || rows * count > kMaxRows)
+      throw std::invalid_argument("A batched verify takes sessions * rows <= 16 tokens and one result per session");
+    ei_session& lead = *batch->sessions[0];
+    require_device(lead);
+    const size_t vocab = lead.model->config.vocab_size;
+    for (ei_session* s : batch->sessions) {
+      require_usable(*s);
+      if (!s->history_ready) throw std::logic_error("Verify requires successful prefill");
+      if (s->context + rows > s->capacity) throw LengthError("Verify rows exceed session capacity");
+    }
+    for (size_t i = 0; i < rows * count; ++i)
+      if (host_tokens[i] >= vocab) throw std::invalid_argument("Token exceeds vocabulary");
+    try {
+      // Work queued on the other sessions' own streams must be done before the shared step touches their state.
+      for (size_t j = 1; j < count; ++j) synchronize(*batch->sessions[j]);
+      std::memcpy(lead.host_tokens, host_tokens, rows * count * 4);
+      EI_CUDA(cudaMemcpyAsync(lead.tokens, lead.host_tokens, rows * count * 4, cudaMemcpyHostToDevice, lead.stream));
+      submit_batch_step(*batch, int(rows));
+      for (ei_session* s : batch->sessions)
+        EI_CUDA(cudaMemcpyAsync(s->host_control, s->control, sizeof(Control), cudaMemcpyDeviceToHost, lead.stream));
+      synchronize(lead);
+      for (ei_session* s : batch->sessions) s->context = size_t(s->host_control->context);
+      for (ei_session* s : batch->sessions)
+        if (s->host_control->status) {
+          const int status = s->host_control->status, zero = 0;
+          EI_CUDA(cudaMemcpyAsync(&s->control->status, &zero, sizeof(int), cudaMemcpyHostToDevice, lead.stream));
+          synchronize(lead);
+          if (status & 2) throw std::invalid_argument("Session token id exceeds vocabulary");
+          if (status & 4) throw std::runtime_error("A bounded wait inside a kernel gave up");
+          throw LengthError("Session context capacity exhausted");
+        }
+    } catch (...) {
+      for (ei_session* s : batch->sessions) drain_failed(*s);
+      throw;
+    }
+    for (size_t j = 0; j < count; ++j) results[j] = batch->sessions[j]->host_control->last;
   });
 }
 

@@ -249,3 +249,41 @@ def speculative_generate(session: Session, prompt: Sequence[int], drafts_for, ma
         emitted.extend(tokens)
         pending = tokens[-1]
     return emitted, accepts
+
+
+class SessionBatch:
+    """Sessions of one model verified in one forward (weights streamed once for all of them); every session ends
+    exactly as after its own Session.verify. sessions * rows <= 16."""
+
+    def __init__(self, sessions: Sequence["Session"]):
+        self._lib = abi.load_library()
+        self.sessions = list(sessions)
+        handles = (C.c_void_p * len(self.sessions))(*[s._handle for s in self.sessions])
+        out = C.c_void_p()
+        abi.check(self._lib.ei_batch_create(handles, len(self.sessions), C.byref(out)))
+        self._handle = out
+
+    def verify(self, tokens: Sequence[Sequence[int]]) -> List[VerifyOutput]:
+        """tokens[j] = [pending, d1..dk] of session j (all of one length)."""
+        ids = np.ascontiguousarray(tokens, dtype=np.uint32)
+        if ids.ndim != 2 or ids.shape[0] != len(self.sessions):
+            raise ValueError("one token row per session")
+        results = (abi.VerifyResult * len(self.sessions))()
+        abi.check(self._lib.ei_batch_verify(self._handle, ids.ctypes.data_as(C.c_void_p), ids.shape[1], results))
+        outputs = []
+        for r in results:
+            targets = [int(r.tokens[i]) for i in range(ids.shape[1])]
+            outputs.append(VerifyOutput(r.emitted, r.context, targets, targets[:r.emitted]))
+        return outputs
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.ei_batch_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+

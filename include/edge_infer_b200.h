@@ -242,6 +242,20 @@ ei_status ei_session_decode(ei_session* session, uint32_t token, const void** lo
  * borrowed BF16 [rows, vocab] view. */
 ei_status ei_session_verify(ei_session* session, const uint32_t* host_tokens, size_t rows,
                             ei_verify_result* result, const void** logits);
+/* ---- several sessions in one forward --------------------------------------------------------------
+ * No counterpart in the reference, whose sessions run one at a time. A batch is a fixed set of sessions of
+ * one model (same device, same capacity, each listed once): ei_batch_verify stacks `rows` tokens of each
+ * into one forward of sessions * rows <= 16 rows, so every weight is streamed once for all of them, while
+ * attention, KV append, greedy acceptance and commit / rollback stay per session. host_tokens is
+ * [sessions][rows] ([pending, d1..dk] of each session, in the order given to ei_batch_create), results is
+ * [sessions]. Every session ends exactly as after its own ei_session_verify with the same tokens (same
+ * bits). The step runs on the first session's stream and workspace; the other sessions must not be in use
+ * from other threads during the call. Destroy the batch before its sessions. */
+typedef struct ei_batch ei_batch;
+ei_status ei_batch_create(ei_session* const* sessions, size_t count, ei_batch** out);
+void ei_batch_destroy(ei_batch* batch);
+ei_status ei_batch_verify(ei_batch* batch, const uint32_t* host_tokens, size_t rows, ei_verify_result* results);
+
 /* Asynchronous form for a device-resident loop: row 0 is the pending token kept on the device by the
  * previous step, row i >= 1 is device_drafts[context_length + i - draft_base]: device_drafts[j] is the
  * token proposed for absolute position draft_base + j, and row i of a step sits at position
