@@ -61,7 +61,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
 }
 
 __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   extern __shared__ __align__(128) unsigned char smem[];
   // The context length was written by the previous step; the preceding kernel of this step only appends the
   // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
@@ -85,6 +84,9 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   load_tile(k_smem[0], v_smem[0], k_base, v_base, p.kv_stride, start, end);
   cp_async_commit();
   if (settled) grid_dependency_wait();  // the queries come from the preceding kernel
+  // Only now: a kernel that triggers after its own wait lets its successor's prologue see everything up to the
+  // kernel before this one as complete, which is what the early fetch above relies on.
+  grid_launch_dependents();
 
   // Stacked row i = r * group + hq  ->  query row r, query head kv_head * group + hq.
   const int i_lo = warp * 16 + g, i_hi = i_lo + 8;
@@ -232,11 +234,11 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
 // splits w, w+4, ... and the four partial sums are added in warp order. The order of every addition is
 // fixed, so replays give identical bits.
 __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float weights[64];
   __shared__ float warp_values[4];
   __shared__ float4 partial_out[4][32];
   grid_dependency_wait();
+  grid_launch_dependents();
   const int slot = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = p.rows * p.heads;
@@ -244,6 +246,16 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   const int length = offset + p.rows;
   if (offset < 0 || length > p.capacity) return;
   const int splits = min(64, (length + p.chunk - 1) / p.chunk);
+  // This warp's splits (w, w + 4, ...) are requested together with the maxima and sums, so that the block pays
+  // one trip to memory instead of two.
+  float4 values[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int s = warp + 4 * i;
+    values[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (s < splits)
+      values[i] = *reinterpret_cast<const float4*>(p.scratch + (size_t(s) * slots + slot) * kPartial + 4 * lane);
+  }
   float m = -INFINITY, l = 0.0f;
   if (int(threadIdx.x) < splits) {
     const float* src = p.scratch + (size_t(threadIdx.x) * slots + slot) * kPartial;
@@ -260,14 +272,16 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   __syncthreads();
   if (lane == 0) warp_values[warp] = denominator;
   float4 accumulator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll 4
-  for (int s = warp; s < splits; s += 4) {
-    const float4 value = *reinterpret_cast<const float4*>(p.scratch + (size_t(s) * slots + slot) * kPartial + 4 * lane);
-    const float w = weights[s];
-    accumulator.x += value.x * w;
-    accumulator.y += value.y * w;
-    accumulator.z += value.z * w;
-    accumulator.w += value.w * w;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int s = warp + 4 * i;
+    if (s < splits) {
+      const float w = weights[s];
+      accumulator.x += values[i].x * w;
+      accumulator.y += values[i].y * w;
+      accumulator.z += values[i].z * w;
+      accumulator.w += values[i].w * w;
+    }
   }
   partial_out[warp][lane] = accumulator;
   __syncthreads();

@@ -141,7 +141,6 @@ __host__ __device__ inline AwqLayout awq_layout(const AwqLaunch& cfg) {
 template <bool kHigh>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     awq_tma_kernel(const __grid_constant__ AwqTensorMaps maps, const GemmParams p, const AwqLaunch cfg) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   constexpr int kBlock = 136;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_address(smem_raw) & 1023u)) & 1023u);
@@ -258,6 +257,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0)
     for (int ph = kAwqEarlyPhases; ph < ring_phases; ++ph) issue(ph);
   __syncthreads();  // barriers initialised; up-front scales / zeros visible
+  grid_launch_dependents();
   if (cfg.tma_sz && !mbarrier_wait(sz_full, 0)) {
     if (p.status) atomicOr(p.status, 4);
     return;  // the whole block sees the same incomplete phase

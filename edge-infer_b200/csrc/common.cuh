@@ -79,6 +79,11 @@ __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 // Allow the dependent kernel to begin launching (its own wait still orders data).
+// Rule kept by every kernel of this library: trigger only after the kernel's own grid_dependency_wait().
+// Then, whenever the code a successor runs before ITS wait executes, everything up to this kernel's
+// predecessor has completed, so such code may read weights, tables and anything written two or more
+// kernels earlier (the context length, settled KV rows) - and nothing newer. Triggering at entry would let
+// a chain of kernels run ahead of work that is still in flight.
 __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

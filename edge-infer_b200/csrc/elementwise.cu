@@ -28,7 +28,6 @@ __device__ __forceinline__ float block_sum(float v, float* shared) {
 
 __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const bf16* in, const bf16* weight,
                                                                bf16* out, int width, float eps) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float shared[32];
   grid_dependency_wait();
   const bf16* x = in + size_t(blockIdx.x) * width;
@@ -43,6 +42,7 @@ __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const bf16* in, 
   }
   const float total = block_sum(sum, shared);
   const float inv = rsqrtf(total / float(width) + eps);
+  grid_launch_dependents();
 #pragma unroll
   for (int j = 0; j < kNormMaxPerThread; ++j) {
     const int i = threadIdx.x + j * kNormThreads;
@@ -51,20 +51,17 @@ __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const bf16* in, 
 }
 
 __global__ void add_kernel(const bf16* a, const bf16* b, bf16* out, size_t count) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
     out[i] = __float2bfloat16_rn(__bfloat162float(a[i]) + __bfloat162float(b[i]));
 }
 
 __global__ void silu_multiply_kernel(const bf16* gate, const bf16* up, bf16* out, size_t count) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
     out[i] = __float2bfloat16_rn(silu_multiply_value(__bfloat162float(gate[i]), __bfloat162float(up[i])));
 }
 
 __global__ void gather_kernel(const uint32_t* ids, const bf16* table, bf16* out, size_t count, size_t width,
                               size_t vocabulary) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x) {
     const uint32_t token = ids[i / width];
     out[i] = token < vocabulary ? table[size_t(token) * width + i % width] : __float2bfloat16_rn(0.0f);
@@ -81,7 +78,6 @@ __device__ __forceinline__ void rotate_pair(float x, float y, float sine, float 
 
 __global__ void rope_kernel(bf16* data, size_t row_stride, size_t head_dim, const float* table,
                             size_t table_stride, size_t offset, const size_t* offsets, const int* pingpong) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   const size_t pair = threadIdx.x, half = head_dim / 2;
   if (pair >= half) return;
   const size_t position = blockIdx.x + (offsets ? offsets[pingpong ? *pingpong : 0] : offset);
@@ -96,7 +92,6 @@ __global__ void rope_kernel(bf16* data, size_t row_stride, size_t head_dim, cons
 
 __global__ void store_kv_kernel(const bf16* source, bf16* cache, size_t count, size_t rows, size_t width,
                                 size_t capacity, size_t offset, const size_t* device_offset) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   const size_t start_row = device_offset ? *device_offset : offset;
   if (start_row > capacity || rows > capacity - start_row) return;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
@@ -104,7 +99,6 @@ __global__ void store_kv_kernel(const bf16* source, bf16* cache, size_t count, s
 }
 
 __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float shared[32];
   __shared__ uint32_t token_shared;
   grid_dependency_wait();
@@ -146,6 +140,7 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
   }
   const float total = block_sum(sum, shared);
   const float inv = rsqrtf(total / float(p.hidden) + p.eps);
+  grid_launch_dependents();
 #pragma unroll
   for (int j = 0; j < kNormMaxPerThread; ++j) {
     const int i = threadIdx.x + j * kNormThreads;
@@ -157,7 +152,6 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
 // One warp per (row, head); lane l owns rotation pairs 2l and 2l+1, i.e. elements
 // {2l, 2l+1} of the first half and {64+2l, 64+2l+1} of the second.
 __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   grid_dependency_wait();
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -206,7 +200,6 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams
 }
 
 __global__ void __launch_bounds__(kNormThreads) residual_norm_kernel(const ResidualNormParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float shared[32];
   grid_dependency_wait();
   const int row = blockIdx.x;
@@ -230,6 +223,7 @@ __global__ void __launch_bounds__(kNormThreads) residual_norm_kernel(const Resid
   }
   const float total = block_sum(sum, shared);
   const float inv = rsqrtf(total / float(p.hidden) + p.eps);
+  grid_launch_dependents();
 #pragma unroll
   for (int j = 0; j < kNormMaxPerThread; ++j) {
     const int i = threadIdx.x + j * kNormThreads;
@@ -256,7 +250,6 @@ __device__ __forceinline__ void store4_bf16(bf16* p, float4 v) {
 }
 
 __global__ void __launch_bounds__(kRowThreads) residual_norm_vec_kernel(const ResidualNormParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float shared[32];
   grid_dependency_wait();
   const int row = blockIdx.x;
@@ -297,6 +290,7 @@ __global__ void __launch_bounds__(kRowThreads) residual_norm_vec_kernel(const Re
   }
   const float total = block_sum(sum, shared);
   const float inv = rsqrtf(total / float(p.hidden) + p.eps);
+  grid_launch_dependents();
 #pragma unroll
   for (int j = 0; j < kRowGroups; ++j) {
     const int i = (threadIdx.x + j * kRowThreads) * 4;

@@ -41,7 +41,6 @@ struct PreparedLinear {
 };
 
 __global__ void commit_rows_kernel(Control* control, int rows) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   grid_dependency_wait();
   if (threadIdx.x || blockIdx.x) return;
   if (control->status & 1) return;
@@ -49,7 +48,6 @@ __global__ void commit_rows_kernel(Control* control, int rows) {
 }
 
 __global__ void silu_pair_rows_kernel(const bf16* gate_up, int rows, int ffn, bf16* out) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   grid_dependency_wait();
   const int total = rows * ffn;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -63,7 +61,6 @@ __global__ void silu_pair_rows_kernel(const bf16* gate_up, int rows, int ffn, bf
 // launch_residual_norm for shapes the streaming GEMM does not take.
 __global__ void __launch_bounds__(512) residual_norm_bf16_kernel(const bf16* projection, int hidden, bf16* residual,
                                                                 const bf16* norm_weight, float eps, bf16* normed) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float shared[32];
   grid_dependency_wait();
   const int row = blockIdx.x;

@@ -23,7 +23,6 @@ __device__ __forceinline__ void take_better(float& best, int& index, float value
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(const bf16* logits, int vocab,
                                                                         size_t row_stride, float* best_value,
                                                                         int* best_index) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ float values[kArgmaxThreads / 32];
   __shared__ int indices[kArgmaxThreads / 32];
   grid_dependency_wait();
@@ -114,7 +113,6 @@ __device__ void accept_commit(const uint32_t* chosen, int rows, const uint32_t* 
 
 __global__ void accept_kernel(const uint32_t* inputs, const uint32_t* targets, int rows, int32_t* context_length,
                               uint32_t* pending, ei_verify_result* result) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   if (threadIdx.x || blockIdx.x) return;
   uint32_t chosen[16];
   for (int i = 0; i < rows; ++i) chosen[i] = targets[i];
@@ -126,7 +124,6 @@ __global__ void __launch_bounds__(512) finalize_kernel(const float* best_value, 
                                                        int rows, uint32_t* targets, const uint32_t* step_tokens,
                                                        Control* control, int32_t* context_length,
                                                        uint32_t* pending, ei_verify_result* result) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   __shared__ uint32_t chosen[16];
   grid_dependency_wait();
   const int row = threadIdx.x >> 5, lane = threadIdx.x & 31;

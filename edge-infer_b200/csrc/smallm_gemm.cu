@@ -9,7 +9,6 @@ namespace ei {
 
 __global__ void splitk_store_kernel(const float* partial, int ksplit, int M, int N, const bf16* bias,
                                     bf16* out, int out_stride) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   grid_dependency_wait();
   const int total = M * N;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -24,7 +23,6 @@ __global__ void splitk_store_kernel(const float* partial, int ksplit, int M, int
 __global__ void awq_generic_kernel(const bf16* x, int x_stride, const int32_t* qweight, const bf16* scales,
                                    const int32_t* zeros, const bf16* bias, bf16* out, int out_stride,
                                    int rows, int N, int K, int group_size, int padded_groups) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   const size_t count = size_t(rows) * N;
   const int weight_stride = (K + 7) / 8, zero_stride = (K / group_size + 7) / 8;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
@@ -46,7 +44,6 @@ __global__ void awq_generic_kernel(const bf16* x, int x_stride, const int32_t* q
 __global__ void dense_generic_kernel(const bf16* x, int x_stride, const bf16* w, long long stride_k,
                                      long long stride_n, const bf16* bias, bf16* out, int out_stride,
                                      int rows, int N, int K) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   const size_t count = size_t(rows) * N;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
        i += size_t(gridDim.x) * blockDim.x) {

@@ -161,7 +161,6 @@ __device__ __forceinline__ void mma_cell(float (&acc)[4], const CellFragments<kH
 
 template <bool kHigh, int kUnits, int kDepth>
 __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const GemmParams p) {
-  grid_launch_dependents();  // let the next kernel start its own prologue; its wait still orders the data
   constexpr int kUnitK = 64;
   constexpr int kParts = 4;             // reduction parts per output: a warp's lanes are 4 parts x 8 elements
   constexpr int kBlock = 136;           // floats per warp in the partial buffer: 128 + 8 keeps loads conflict-free
@@ -222,6 +221,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) smallm_gemm_kernel(const Gemm
   unsigned char* x_hi = x_lo + size_t(units) * kUnitK * 16;
   stage_activations(p, x_lo, x_hi, kHigh, unit_begin * kUnitK, units * kUnitK);
   __syncthreads();
+  grid_launch_dependents();
 
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
   const int e = warp * 8 + (lane & 7);
