@@ -152,39 +152,49 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
 // One warp per (row, head); lane l owns rotation pairs 2l and 2l+1, i.e. elements
 // {2l, 2l+1} of the first half and {64+2l, 64+2l+1} of the second.
 __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams p) {
-  grid_dependency_wait();
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int per_row = p.heads + 2 * p.kv_heads;
   if (warp_global >= p.rows * per_row) return;
   const int row = warp_global / per_row, slot = warp_global - row * per_row;
+  // Read before waiting for the projection: the context length (written by the previous step), the norm
+  // weights and the rotation table do not come from it, so their latency overlaps its tail.
   const int context = p.control->context;
   const int position = context + row;
   if (context + p.rows > p.capacity || position >= p.max_positions) return;  // status set by the embed kernel
+  const bool is_value = slot >= p.heads + p.kv_heads;
+  const bool is_query = slot < p.heads;
+  const bf16* norm = is_query ? p.q_norm : p.k_norm;
+  uint32_t wl = 0, wh = 0;
+  float4 trig = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (!is_value) {
+    if (norm) {
+      wl = *reinterpret_cast<const uint32_t*>(norm + 2 * lane);
+      wh = *reinterpret_cast<const uint32_t*>(norm + 64 + 2 * lane);
+    }
+    trig = *reinterpret_cast<const float4*>(p.rope_table + size_t(position) * 128 + 4 * lane);
+  }
+  grid_dependency_wait();
+  grid_launch_dependents();
   bf16* head = p.qkv + size_t(row) * p.qkv_stride + size_t(slot) * 128;
-  if (slot >= p.heads + p.kv_heads) {  // value head: append as is
+  if (is_value) {  // value head: append as is
     const int kvh = slot - p.heads - p.kv_heads;
     const uint2 v = *reinterpret_cast<const uint2*>(head + lane * 4);
     *reinterpret_cast<uint2*>(p.v_cache + (size_t(position) * p.kv_heads + kvh) * 128 + lane * 4) = v;
     return;
   }
-  const bool is_query = slot < p.heads;
   const uint32_t lo = *reinterpret_cast<const uint32_t*>(head + 2 * lane);
   const uint32_t hi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
   float x0 = bf16_lo(lo), x1 = bf16_hi(lo), y0 = bf16_lo(hi), y1 = bf16_hi(hi);
-  const bf16* norm = is_query ? p.q_norm : p.k_norm;
   if (norm) {
     float sum = fmaf(x0, x0, fmaf(x1, x1, fmaf(y0, y0, y1 * y1)));
     sum = warp_sum(sum);
     const float inv = rsqrtf(sum / 128.0f + p.eps);
-    const uint32_t wl = *reinterpret_cast<const uint32_t*>(norm + 2 * lane);
-    const uint32_t wh = *reinterpret_cast<const uint32_t*>(norm + 64 + 2 * lane);
     x0 = round_bf16(round_bf16(x0 * inv) * bf16_lo(wl));
     x1 = round_bf16(round_bf16(x1 * inv) * bf16_hi(wl));
     y0 = round_bf16(round_bf16(y0 * inv) * bf16_lo(wh));
     y1 = round_bf16(round_bf16(y1 * inv) * bf16_hi(wh));
   }
-  const float4 trig = *reinterpret_cast<const float4*>(p.rope_table + size_t(position) * 128 + 4 * lane);
   float a0, b0, a1, b1;
   rotate_pair(x0, y0, trig.x, trig.y, a0, b0);
   rotate_pair(x1, y1, trig.z, trig.w, a1, b1);
@@ -236,7 +246,7 @@ __global__ void __launch_bounds__(kNormThreads) residual_norm_kernel(const Resid
 // features. Every load of a thread (partial slices, bias, residual) is issued before the first use, so a
 // row costs about one memory latency instead of one per slice.
 constexpr int kRowThreads = 1024;
-constexpr int kRowGroups = 3;  // 1024 * 4 * 3 >= 10240
+constexpr int kRowMaxGroups = 3;  // 1024 threads * 4 values * 3 groups >= 10240
 
 __device__ __forceinline__ float4 load4_bf16(const bf16* p) {
   const uint2 raw = *reinterpret_cast<const uint2*>(p);
@@ -249,28 +259,43 @@ __device__ __forceinline__ void store4_bf16(bf16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// kRowGroups: groups of 4096 values a row needs (1 for hidden <= 4096), so that small rows keep few registers.
+template <int kRowGroups>
 __global__ void __launch_bounds__(kRowThreads) residual_norm_vec_kernel(const ResidualNormParams p) {
   __shared__ float shared[32];
-  grid_dependency_wait();
   const int row = blockIdx.x;
   bf16* residual = p.residual + size_t(row) * p.hidden;
   bf16* normed = p.normed + size_t(row) * p.hidden;
   const size_t slice = size_t(p.rows) * p.hidden;
   const float* partial = p.partial + size_t(row) * p.hidden;
+  const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  // Before waiting for the projection: the residual stream (last written several kernels ago), the bias and
+  // the norm weights do not come from it.
+  float4 old_residual[kRowGroups], bias[kRowGroups], weight[kRowGroups];
+#pragma unroll
+  for (int j = 0; j < kRowGroups; ++j) {
+    const int i = (threadIdx.x + j * kRowThreads) * 4;
+    old_residual[j] = bias[j] = weight[j] = zero;
+    if (i < p.hidden) {
+      old_residual[j] = load4_bf16(residual + i);
+      if (p.bias) bias[j] = load4_bf16(p.bias + i);
+      weight[j] = load4_bf16(p.norm_weight + i);
+    }
+  }
+  grid_dependency_wait();
+  grid_launch_dependents();
   float4 values[kRowGroups];
   float sum = 0.0f;
 #pragma unroll
   for (int j = 0; j < kRowGroups; ++j) {
     const int i = (threadIdx.x + j * kRowThreads) * 4;
-    values[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    values[j] = zero;
     if (i < p.hidden) {
-      const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       const float4 a0 = *reinterpret_cast<const float4*>(partial + i);
       const float4 a1 = p.ksplit > 1 ? *reinterpret_cast<const float4*>(partial + slice + i) : zero;
       const float4 a2 = p.ksplit > 2 ? *reinterpret_cast<const float4*>(partial + 2 * slice + i) : zero;
       const float4 a3 = p.ksplit > 3 ? *reinterpret_cast<const float4*>(partial + 3 * slice + i) : zero;
-      const float4 r = load4_bf16(residual + i);
-      const float4 b = p.bias ? load4_bf16(p.bias + i) : zero;
+      const float4 r = old_residual[j], b = bias[j];
       float4 projection = make_float4(a0.x + a1.x, a0.y + a1.y, a0.z + a1.z, a0.w + a1.w);
       projection = make_float4(projection.x + a2.x, projection.y + a2.y, projection.z + a2.z, projection.w + a2.w);
       projection = make_float4(projection.x + a3.x, projection.y + a3.y, projection.z + a3.z, projection.w + a3.w);
@@ -290,12 +315,11 @@ __global__ void __launch_bounds__(kRowThreads) residual_norm_vec_kernel(const Re
   }
   const float total = block_sum(sum, shared);
   const float inv = rsqrtf(total / float(p.hidden) + p.eps);
-  grid_launch_dependents();
 #pragma unroll
   for (int j = 0; j < kRowGroups; ++j) {
     const int i = (threadIdx.x + j * kRowThreads) * 4;
     if (i < p.hidden) {
-      const float4 w = load4_bf16(p.norm_weight + i);
+      const float4 w = weight[j];
       float4 out;
       out.x = round_bf16(values[j].x * inv) * w.x;
       out.y = round_bf16(values[j].y * inv) * w.y;
@@ -360,10 +384,15 @@ void launch_qk_norm_rope_store(const QkvParams& p, cudaStream_t stream, bool pdl
 }
 
 void launch_residual_norm(const ResidualNormParams& p, cudaStream_t stream, bool pdl) {
-  if (p.hidden % 4 == 0)
-    launch(residual_norm_vec_kernel, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
-  else
+  if (p.hidden % 4 != 0) {
     launch(residual_norm_kernel, dim3(p.rows), dim3(kNormThreads), 0, stream, pdl, p);
+  } else if (p.hidden <= kRowThreads * 4) {
+    launch(residual_norm_vec_kernel<1>, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
+  } else if (p.hidden <= kRowThreads * 8) {
+    launch(residual_norm_vec_kernel<2>, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
+  } else {
+    launch(residual_norm_vec_kernel<kRowMaxGroups>, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
+  }
 }
 
 }  // namespace ei
