@@ -138,7 +138,10 @@ __host__ __device__ inline AwqLayout awq_layout(const AwqLaunch& cfg) {
   return l;
 }
 
-template <bool kHigh>
+// kPair: SwiGLU pair epilogue; kTmaSz: scales / zero points staged by TMA boxes; kFull: every warp owns a unit
+// of the K slice (slices of 4096 inputs). The three are compile-time so that the loop, which is issue-bound,
+// carries no branch or uniform-register arithmetic for them.
+template <bool kHigh, bool kPair, bool kTmaSz, bool kFull>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     awq_tma_kernel(const __grid_constant__ AwqTensorMaps maps, const GemmParams p, const AwqLaunch cfg) {
   constexpr int kBlock = 136;
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int unit_begin = slice * kAwqSliceUnits;
   const int units = min(kAwqSliceUnits, units_total - unit_begin);
   const int tiles = p.N / 8;
-  const bool pair = p.epilogue == kEpiSiluPair;
+  constexpr bool pair = kPair;
   const int chunks = pair ? tiles / 2 : tiles;
   const int per_chunk = pair ? 2 : 1;
   const int item_begin = int((long long)group * chunks / groups) * per_chunk;
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     mbarrier_init(sz_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (cfg.tma_sz) {
+    if (kTmaSz) {
       // Group scales and packed zero points of every row this block will touch: one box each (two in pair
       // mode: the gate rows and the up rows). Rows past the matrix read as zero and are never used.
       mbarrier_expect_tx(sz_full, uint32_t(cfg.sz_boxes * cfg.sz_rows * (scale_pitch + zero_pitch)));
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int ph = 0; ph < kAwqEarlyPhases && ph < ring_phases; ++ph) issue(ph);
   }
 
-  if (!cfg.tma_sz) {
+  if (!kTmaSz) {
     // Scales (BF16) and zero nibbles (one byte each) of every tile of this block: [item][row][group].
     // Four elements per thread per round, all eight loads issued before the first store, so a round costs
     // one memory latency.
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   grid_dependency_wait();
 
   // A fragments of this warp's 256 inputs, pinned in registers.
-  const bool live = warp < units;
+  const bool live = kFull || warp < units;
   CellFragments<kHigh> frag[8];
   {
     // Cell `cell` of lane (g, c) holds inputs [32 cell + 8 c, + 8) of the unit: the four lanes of a row read
@@ -258,7 +261,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int ph = kAwqEarlyPhases; ph < ring_phases; ++ph) issue(ph);
   __syncthreads();  // barriers initialised; up-front scales / zeros visible
   grid_launch_dependents();
-  if (cfg.tma_sz && !mbarrier_wait(sz_full, 0)) {
+  if (kTmaSz && !mbarrier_wait(sz_full, 0)) {
     if (p.status) atomicOr(p.status, 4);
     return;  // the whole block sees the same incomplete phase
   }
@@ -278,11 +281,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t lane_word = uint32_t(warp * 1024 + g * 128 + (g << 4) + c * 4);
   // Scales / zero points of this lane's row and groups: TMA mode [box][row][group], up-front mode [item][...].
   const uint32_t sz_address = smem_address(sz);
-  const uint32_t lane_scale = cfg.tma_sz ? sz_address + g * scale_pitch + unit_group * 2
+  const uint32_t lane_scale = kTmaSz ? sz_address + g * scale_pitch + unit_group * 2
                                          : sz_address + (g * cfg.units_box * 2 + unit_group) * 2;
-  const uint32_t lane_zero = cfg.tma_sz ? sz_address + layout.sz_scale_bytes + g * zero_pitch + (unit_group >> 3) * 4
+  const uint32_t lane_zero = kTmaSz ? sz_address + layout.sz_scale_bytes + g * zero_pitch + (unit_group >> 3) * 4
                                         : sz_address + 8 * cfg.units_box * 2 * 2 + g * cfg.units_box * 2 + unit_group;
-  const int zero_shift = cfg.tma_sz ? (unit_group & 7) * 4 : 0;
+  const int zero_shift = kTmaSz ? (unit_group & 7) * 4 : 0;
   // Row of tile t (0 or 1) of phase `step` in the staged scale / zero rows.
   const int phase_rows = pair ? 8 : 16, second_rows = pair ? cfg.sz_rows : 8;
 
@@ -295,11 +298,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // One tile: 8 words per lane, two accumulator chains so consecutive MMAs do not wait on each other.
   // `tile_address`: the staged tile; `step`, `t`: phase and tile within the phase.
   auto compute_tile = [&](uint32_t tile_address, int step, int t, float (&acc)[4]) {
-    float other[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
-    if (!live) return;
+    float other[4];
+    if (!live) {
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+      return;
+    }
     uint32_t scale2[2], zero2[2];
-    if (cfg.tma_sz) {
+    if (kTmaSz) {
       const int sz_row = step * phase_rows + t * second_rows;
       const uint32_t zero_word = shared_u32(lane_zero + sz_row * zero_pitch);
       const uint32_t scales = shared_u32(lane_scale + sz_row * scale_pitch);
@@ -327,8 +332,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t b1 = dequant_pair(word >> 4, z, sc);
       const uint32_t b2 = dequant_pair(word >> 8, z, sc);
       const uint32_t b3 = dequant_pair(word >> 12, z, sc);
-      mma_cell<kHigh>(acc, frag[cell], 0, b0, b1);
-      mma_cell<kHigh>(other, frag[cell], 1, b2, b3);
+      if (cell == 0) {  // the first MMA of each chain starts from zero: no clearing of the accumulators
+        mma_cell<kHigh, true>(acc, frag[cell], 0, b0, b1);
+        mma_cell<kHigh, true>(other, frag[cell], 1, b2, b3);
+      } else {
+        mma_cell<kHigh>(acc, frag[cell], 0, b0, b1);
+        mma_cell<kHigh>(other, frag[cell], 1, b2, b3);
+      }
     }
     acc[0] += other[0]; acc[1] += other[1]; acc[2] += other[2]; acc[3] += other[3];
   };
@@ -394,8 +404,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t tile_address = stages_address + uint32_t(slot * kAwqPhaseTiles) * layout.weight_bytes;
     if (ok) compute_tile(tile_address, step, 0, acc[0]);
     if (ok && pending >= 0) finish(pending, loaded);
-    acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
-    if (ok && index + 1 < item_count) compute_tile(tile_address + layout.weight_bytes, step, 1, acc[1]);
+    if (ok && (kPair || index + 1 < item_count))  // pairs come whole
+      compute_tile(tile_address + layout.weight_bytes, step, 1, acc[1]);
+    else
+      acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
     if (++slot == ring_phases) {
       slot = 0;
       parity ^= 1;

@@ -155,6 +155,36 @@ void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void
 
 bool aligned_16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+template <bool kHigh, bool kPair, bool kTmaSz, bool kFull>
+void launch_awq_instance(int grid, size_t smem, cudaStream_t stream, bool pdl, const AwqTensorMaps& maps,
+                         const GemmParams& p, const AwqLaunch& cfg) {
+  auto kernel = awq_tma_kernel<kHigh, kPair, kTmaSz, kFull>;
+  static thread_local int configured_device = -1;
+  int device = 0;
+  EI_CUDA(cudaGetDevice(&device));
+  if (configured_device != device) {
+    EI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_device = device;
+  }
+  launch(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, pdl, maps, p, cfg);
+}
+
+// The instances that exist: TMA-staged scales with or without full slices, and the up-front fallback.
+template <bool kHigh, bool kPair>
+void dispatch_awq_staging(bool tma_sz, bool full, int grid, size_t smem, cudaStream_t stream, bool pdl,
+                          const AwqTensorMaps& maps, const GemmParams& p, const AwqLaunch& cfg) {
+  if (tma_sz && full) return launch_awq_instance<kHigh, kPair, true, true>(grid, smem, stream, pdl, maps, p, cfg);
+  if (tma_sz) return launch_awq_instance<kHigh, kPair, true, false>(grid, smem, stream, pdl, maps, p, cfg);
+  return launch_awq_instance<kHigh, kPair, false, false>(grid, smem, stream, pdl, maps, p, cfg);
+}
+void dispatch_awq(bool high, bool pair, bool tma_sz, bool full, int grid, size_t smem, cudaStream_t stream, bool pdl,
+                  const AwqTensorMaps& maps, const GemmParams& p, const AwqLaunch& cfg) {
+  if (high && pair) return dispatch_awq_staging<true, true>(tma_sz, full, grid, smem, stream, pdl, maps, p, cfg);
+  if (high) return dispatch_awq_staging<true, false>(tma_sz, full, grid, smem, stream, pdl, maps, p, cfg);
+  if (pair) return dispatch_awq_staging<false, true>(tma_sz, full, grid, smem, stream, pdl, maps, p, cfg);
+  return dispatch_awq_staging<false, false>(tma_sz, full, grid, smem, stream, pdl, maps, p, cfg);
+}
+
 void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, bool pdl) {
   const int units_total = p.K / 256;
   AwqLaunch cfg{};
@@ -196,18 +226,8 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
                CU_TENSOR_MAP_SWIZZLE_NONE, "zero points");
   }
 
-  static thread_local int configured_device = -1;
-  int device = 0;
-  EI_CUDA(cudaGetDevice(&device));
-  if (configured_device != device) {
-    EI_CUDA(cudaFuncSetAttribute(awq_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    EI_CUDA(cudaFuncSetAttribute(awq_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    configured_device = device;
-  }
-  if (plan.high)
-    launch(awq_tma_kernel<true>, dim3(plan.grid), dim3(kGemmThreads), smem, stream, pdl, maps, p, cfg);
-  else
-    launch(awq_tma_kernel<false>, dim3(plan.grid), dim3(kGemmThreads), smem, stream, pdl, maps, p, cfg);
+  const bool full = units_total % kAwqSliceUnits == 0;
+  dispatch_awq(plan.high, pair, cfg.tma_sz != 0, full && cfg.tma_sz != 0, plan.grid, smem, stream, pdl, maps, p, cfg);
 }
 
 }  // namespace

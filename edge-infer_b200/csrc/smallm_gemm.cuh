@@ -150,13 +150,20 @@ __device__ __forceinline__ void load_cell(CellFragments<kHigh>& f, const bf16* x
   }
 }
 
-template <bool kHigh>
+template <bool kHigh, bool kFirst = false>
 __device__ __forceinline__ void mma_cell(float (&acc)[4], const CellFragments<kHigh>& f, int which, uint32_t b0,
                                          uint32_t b1) {
-  if (kHigh)
-    mma_bf16_16816(acc, f.a[which][0], f.a[which][1], f.a[which][2], f.a[which][3], b0, b1);
-  else
-    mma_bf16_16816(acc, f.a[which][0], 0u, f.a[which][1], 0u, b0, b1);
+  if (kFirst) {
+    if (kHigh)
+      mma_bf16_16816_first(acc, f.a[which][0], f.a[which][1], f.a[which][2], f.a[which][3], b0, b1);
+    else
+      mma_bf16_16816_first(acc, f.a[which][0], 0u, f.a[which][1], 0u, b0, b1);
+  } else {
+    if (kHigh)
+      mma_bf16_16816(acc, f.a[which][0], f.a[which][1], f.a[which][2], f.a[which][3], b0, b1);
+    else
+      mma_bf16_16816(acc, f.a[which][0], 0u, f.a[which][1], 0u, b0, b1);
+  }
 }
 
 template <bool kHigh, int kUnits, int kDepth>
