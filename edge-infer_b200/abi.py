@@ -131,6 +131,12 @@ PROTOTYPES = {
     "ei_batch_create": (_S, [C.POINTER(_P), _Z, C.POINTER(_P)]),
     "ei_batch_destroy": (None, [_P]),
     "ei_batch_verify": (_S, [_P, _P, _Z, C.POINTER(VerifyResult)]),
+    "ei_speculative_create": (_S, [_P, _P, _Z, C.POINTER(_P)]),
+    "ei_speculative_destroy": (None, [_P]),
+    "ei_speculative_prefill": (_S, [_P, _P, _Z, C.POINTER(C.c_uint32)]),
+    "ei_speculative_enqueue": (_S, [_P, _Z]),
+    "ei_speculative_drain": (_S, [_P, _P, _Z, C.POINTER(_Z), C.POINTER(VerifyResult)]),
+    "ei_speculative_truncate": (_S, [_P, _Z]),
     "ei_session_verify_enqueue": (_S, [_P, _P, _Z, _Z, _Z]),
     "ei_session_drain": (_S, [_P, C.POINTER(VerifyResult), C.POINTER(C.c_uint64)]),
     "ei_session_truncate": (_S, [_P, _Z]),

@@ -36,6 +36,14 @@ struct DraftSource {
   long long base, count;
 };
 
+// Device-resident description of where a session records what it emits: tokens[position - base] receives the
+// token emitted for absolute position `position` (the token after the first `position` ones). Read at kernel
+// time. A draft session's sink is the array the target session takes its drafts from.
+struct TokenSink {
+  uint32_t* tokens;
+  long long base, count;
+};
+
 struct EmbedParams {
   const uint32_t* tokens;     // host-driven step: [rows] device tokens; null in the device-resident loop
   const DraftSource* source;  // device-resident loop: row 0 = control->pending, row i = draft of position context + i
@@ -110,7 +118,10 @@ void launch_argmax_partials(const bf16* logits, size_t rows, size_t vocab, size_
 void launch_finalize(const float* best_value, const int* best_index, int parts, int rows,
                      uint32_t* targets, const uint32_t* step_tokens, Control* control,
                      int32_t* context_length, uint32_t* pending, ei_verify_result* result,
-                     cudaStream_t stream, bool pdl);
+                     cudaStream_t stream, bool pdl, const TokenSink* sink = nullptr);
+// Makes a draft session continue from where the target session stands: copies context length and pending token
+// and inherits a raised status. One thread.
+void launch_adopt_control(Control* mine, const Control* theirs, cudaStream_t stream);
 
 // Acceptance only, from targets already chosen.
 void launch_accept(const uint32_t* inputs, const uint32_t* targets, int rows, int32_t* context_length,

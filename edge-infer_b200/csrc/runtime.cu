@@ -265,6 +265,7 @@ struct ei_session {
   Control* control = nullptr;
   DraftSource* draft_source = nullptr;
   DraftSource draft_host{nullptr, 0, 0};
+  TokenSink* token_sink = nullptr;  // device; all zero unless a speculative decoder owns the session
   bf16 *k_cache = nullptr, *v_cache = nullptr;
   // pinned host staging
   uint32_t* host_tokens = nullptr;
@@ -286,6 +287,24 @@ struct ei_session {
 struct ei_batch {
   std::vector<ei_session*> sessions;
   cudaGraphExec_t graphs[kMaxRows + 1] = {};  // by rows per session
+};
+
+// A target session and a draft session that generate together without host round trips: per round the draft
+// session decodes drafts_per_round + 1 tokens, each from the token the previous step left on the device, the
+// target session verifies [pending, d1..dk] in one forward, and the draft session adopts the target's context
+// length and pending token. One device array holds the token of every position for both: the draft session
+// writes its proposals into it, the target session reads them from it and overwrites them with what it emits.
+struct ei_speculative {
+  ei_session* target = nullptr;
+  ei_session* draft = nullptr;
+  size_t drafts = 0;             // k: drafts verified per round (rows = k + 1)
+  size_t capacity = 0;           // of both sessions
+  uint32_t* tokens = nullptr;    // device [capacity + kMaxRows + 1]: token of every absolute position
+  size_t token_count = 0;
+  cudaEvent_t drafted = nullptr, verified = nullptr;
+  size_t prompt_rows = 0;
+  size_t bound = 0;              // upper bound of the context length after everything enqueued so far
+  bool started = false;
 };
 
 namespace {
@@ -525,7 +544,7 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
       launch(commit_rows_kernel, dim3(1), dim3(32), 0, s.stream, pdl, s.control, rows);
     } else {
       launch_finalize(s.best_value, s.best_index, parts, rows, s.targets, s.step_tokens, s.control, nullptr, nullptr,
-                      nullptr, s.stream, pdl);
+                      nullptr, s.stream, pdl, s.token_sink);
     }
   }
   s.launches_per_step[rows] = s.launches - before;
@@ -858,6 +877,7 @@ ei_status ei_session_create(ei_model* model, size_t capacity, int graph, ei_sess
     const size_t o_best_value = take(size_t(256) * 16 * sizeof(float)), o_best_index = take(size_t(256) * 16 * sizeof(int));
     const size_t o_tokens = take(kMaxRows * 4), o_step = take(kMaxRows * 4), o_targets = take(kMaxRows * 4);
     const size_t o_control = take(sizeof(Control)), o_source = take(sizeof(DraftSource));
+    const size_t o_sink = take(sizeof(TokenSink));
     const size_t kv_bytes = c.n_layers * capacity * kv_width * 2;
     const size_t o_k = take(kv_bytes), o_v = take(kv_bytes);
     EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&s->arena), offset));
@@ -879,6 +899,7 @@ ei_status ei_session_create(ei_model* model, size_t capacity, int graph, ei_sess
     s->targets = reinterpret_cast<uint32_t*>(base + o_targets);
     s->control = reinterpret_cast<Control*>(base + o_control);
     s->draft_source = reinterpret_cast<DraftSource*>(base + o_source);
+    s->token_sink = reinterpret_cast<TokenSink*>(base + o_sink);
     s->k_cache = reinterpret_cast<bf16*>(base + o_k);
     s->v_cache = reinterpret_cast<bf16*>(base + o_v);
     try {
@@ -887,6 +908,7 @@ ei_status ei_session_create(ei_model* model, size_t capacity, int graph, ei_sess
       EI_CUDA(cudaMallocHost(reinterpret_cast<void**>(&s->host_control), sizeof(Control)));
       EI_CUDA(cudaMemsetAsync(s->control, 0, sizeof(Control), s->stream));
       EI_CUDA(cudaMemsetAsync(s->draft_source, 0, sizeof(DraftSource), s->stream));
+      EI_CUDA(cudaMemsetAsync(s->token_sink, 0, sizeof(TokenSink), s->stream));
       EI_CUDA(cudaStreamSynchronize(s->stream));
     } catch (...) {
       ei_session_destroy(s.release());
@@ -1225,6 +1247,203 @@ ei_status ei_session_read_logits(ei_session* session, size_t rows, void* host_lo
 
 size_t ei_session_launches_per_step(const ei_session* session, size_t rows) {
   return session && rows <= kMaxRows ? session->launches_per_step[rows] : 0;
+}
+
+ei_status ei_speculative_create(ei_session* target, ei_session* draft, size_t drafts_per_round, ei_speculative** out) {
+  return guarded([&] {
+    if (!target || !draft || !out || target == draft)
+      throw std::invalid_argument("A speculative decoder takes a target and a distinct draft session");
+    if (!drafts_per_round || drafts_per_round + 1 > kMaxRows)
+      throw std::invalid_argument("Invalid draft capacity");
+    if (target->model->device != draft->model->device)
+      throw std::invalid_argument("Target and draft sessions must live on one device");
+    if (target->model->config.vocab_size != draft->model->config.vocab_size)
+      throw std::invalid_argument("Target and draft models must share a vocabulary");
+    require_usable(*target);
+    require_usable(*draft);
+    require_device(*target);
+    auto spec = std::make_unique<ei_speculative>();
+    spec->target = target;
+    spec->draft = draft;
+    spec->drafts = drafts_per_round;
+    spec->capacity = std::min(target->capacity, draft->capacity);
+    spec->token_count = spec->capacity + kMaxRows + 1;
+    try {
+      EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&spec->tokens), spec->token_count * sizeof(uint32_t)));
+      EI_CUDA(cudaMemset(spec->tokens, 0, spec->token_count * sizeof(uint32_t)));
+      EI_CUDA(cudaEventCreateWithFlags(&spec->drafted, cudaEventDisableTiming));
+      EI_CUDA(cudaEventCreateWithFlags(&spec->verified, cudaEventDisableTiming));
+      // Both sessions record what they emit in the shared array; the target also takes its drafts from it.
+      const TokenSink sink{spec->tokens, 0, (long long)spec->token_count};
+      const DraftSource source{spec->tokens, 0, (long long)spec->token_count};
+      for (ei_session* s : {target, draft}) {
+        synchronize(*s);
+        EI_CUDA(cudaMemcpyAsync(s->token_sink, &sink, sizeof(sink), cudaMemcpyHostToDevice, s->stream));
+        s->draft_host = source;
+        EI_CUDA(cudaMemcpyAsync(s->draft_source, &source, sizeof(source), cudaMemcpyHostToDevice, s->stream));
+        synchronize(*s);
+      }
+    } catch (...) {
+      ei_speculative_destroy(spec.release());
+      throw;
+    }
+    *out = spec.release();
+  });
+}
+
+void ei_speculative_destroy(ei_speculative* spec) {
+  if (!spec) return;
+  // Detach the sessions from the array before it is freed.
+  const TokenSink none{nullptr, 0, 0};
+  const DraftSource empty{nullptr, 0, 0};
+  for (ei_session* s : {spec->target, spec->draft}) {
+    if (!s || s->poisoned) continue;
+    if (cudaStreamSynchronize(s->stream) != cudaSuccess) continue;
+    cudaMemcpyAsync(s->token_sink, &none, sizeof(none), cudaMemcpyHostToDevice, s->stream);
+    cudaMemcpyAsync(s->draft_source, &empty, sizeof(empty), cudaMemcpyHostToDevice, s->stream);
+    s->draft_host = empty;
+    cudaStreamSynchronize(s->stream);
+  }
+  if (spec->drafted) cudaEventDestroy(spec->drafted);
+  if (spec->verified) cudaEventDestroy(spec->verified);
+  if (spec->tokens) cudaFree(spec->tokens);
+  delete spec;
+}
+
+ei_status ei_speculative_prefill(ei_speculative* spec, const uint32_t* host_tokens, size_t rows, uint32_t* first_token) {
+  return guarded([&] {
+    if (!spec) throw std::invalid_argument("speculative decoder is null");
+    if (!host_tokens || !rows) throw std::invalid_argument("Prompt must be nonempty");
+    if (rows + 1 > spec->capacity) throw LengthError("Prompt exceeds speculative context capacity");
+    ei_session& t = *spec->target;
+    ei_session& d = *spec->draft;
+    spec->started = false;
+    // Both sessions take the whole prompt; the target's greedy token after it is the first generated token and
+    // the pending token of both (ref: runtime/src/speculative_decoder.cpp:244-276).
+    for (ei_session* s : {&t, &d})
+      if (ei_session_prefill(s, host_tokens, rows, nullptr, nullptr) != EI_OK)
+        throw std::runtime_error("Speculative prefill failed: " + g_last_error);
+    try {
+      const size_t last_row = (rows - 1) % kMaxRows;
+      uint32_t first = 0;
+      EI_CUDA(cudaMemcpyAsync(t.host_tokens, t.targets + last_row, sizeof(uint32_t), cudaMemcpyDeviceToHost, t.stream));
+      synchronize(t);
+      first = t.host_tokens[0];
+      if (first >= t.model->config.vocab_size) throw std::runtime_error("Target sampled an invalid token id");
+      for (ei_session* s : {&t, &d}) {
+        EI_CUDA(cudaMemcpyAsync(&s->control->pending, &first, sizeof(first), cudaMemcpyHostToDevice, s->stream));
+        synchronize(*s);
+      }
+      EI_CUDA(cudaMemcpyAsync(spec->tokens, host_tokens, rows * sizeof(uint32_t), cudaMemcpyHostToDevice, t.stream));
+      EI_CUDA(cudaMemcpyAsync(spec->tokens + rows, &first, sizeof(first), cudaMemcpyHostToDevice, t.stream));
+      synchronize(t);
+      if (first_token) *first_token = first;
+    } catch (...) {
+      drain_failed(t);
+      drain_failed(d);
+      throw;
+    }
+    spec->prompt_rows = rows;
+    spec->bound = rows;
+    spec->started = true;
+  });
+}
+
+ei_status ei_speculative_enqueue(ei_speculative* spec, size_t rounds) {
+  return guarded([&] {
+    if (!spec) throw std::invalid_argument("speculative decoder is null");
+    if (!spec->started) throw std::logic_error("Speculative generation requires successful prefill");
+    ei_session& t = *spec->target;
+    ei_session& d = *spec->draft;
+    require_usable(t);
+    require_usable(d);
+    require_device(t);
+    const size_t rows = spec->drafts + 1;
+    // The host does not know the context length between drains: it bounds it by full acceptance. Checked for
+    // all rounds before any is submitted, so a refusal leaves the decoder as it was.
+    if (spec->bound + rounds * rows > spec->capacity) throw LengthError("Speculative rounds exceed session capacity");
+    try {
+      for (size_t round = 0; round < rounds; ++round) {
+        // k + 1 draft steps, each fed by the token the previous one left on the device: d1..dk are verified, the
+        // last step only appends the draft cache row of dk (ref: generate_draft_tokens, speculative_decoder.cpp:176-187).
+        for (size_t step = 0; step < rows; ++step) submit_step(d, 1, kVerifyDevice);
+        EI_CUDA(cudaEventRecord(spec->drafted, d.stream));
+        EI_CUDA(cudaStreamWaitEvent(t.stream, spec->drafted, 0));
+        submit_step(t, int(rows), kVerifyDevice);  // ref: verify_greedy, speculative_decoder.cpp:200-224
+        EI_CUDA(cudaEventRecord(spec->verified, t.stream));
+        EI_CUDA(cudaStreamWaitEvent(d.stream, spec->verified, 0));
+        // Both sessions keep the pending input plus every accepted one (speculative_decoder.cpp:219-223).
+        launch_adopt_control(d.control, t.control, d.stream);
+        spec->bound += rows;
+      }
+    } catch (...) {
+      drain_failed(t);
+      drain_failed(d);
+      spec->started = false;
+      throw;
+    }
+  });
+}
+
+ei_status ei_speculative_drain(ei_speculative* spec, uint32_t* host_tokens, size_t capacity, size_t* count,
+                               ei_verify_result* last) {
+  return guarded([&] {
+    if (!spec) throw std::invalid_argument("speculative decoder is null");
+    if (!spec->started) throw std::logic_error("Speculative generation requires successful prefill");
+    ei_session& t = *spec->target;
+    ei_session& d = *spec->draft;
+    require_usable(t);
+    require_usable(d);
+    try {
+      read_control(d);  // the draft stream ends every round: waiting for it waits for the target too
+      read_control(t);
+      check_status(t);
+      check_status(d);
+      spec->bound = t.context;
+      // Generated so far: the tokens of positions prompt_rows .. context (the last one is pending).
+      const size_t generated = t.context + 1 - spec->prompt_rows;
+      if (count) *count = generated;
+      if (host_tokens && capacity) {
+        const size_t copy = std::min(generated, capacity);
+        EI_CUDA(cudaMemcpyAsync(host_tokens, spec->tokens + spec->prompt_rows, copy * sizeof(uint32_t),
+                                cudaMemcpyDeviceToHost, t.stream));
+        synchronize(t);
+      }
+      if (last) *last = t.host_control->last;
+    } catch (...) {
+      drain_failed(t);
+      drain_failed(d);
+      spec->started = false;
+      throw;
+    }
+  });
+}
+
+ei_status ei_speculative_truncate(ei_speculative* spec, size_t generated) {
+  return guarded([&] {
+    if (!spec) throw std::invalid_argument("speculative decoder is null");
+    if (!spec->started) throw std::logic_error("Speculative generation requires successful prefill");
+    ei_session& t = *spec->target;
+    ei_session& d = *spec->draft;
+    read_control(d);
+    read_control(t);
+    // Keep `generated` generated tokens: the last of them becomes pending, the ones before it stay in both caches
+    // (ref: EOS truncation, speculative_decoder.cpp:302-304).
+    if (!generated || spec->prompt_rows + generated - 1 > t.context)
+      throw std::invalid_argument("Truncation keeps between one and all generated tokens");
+    const int32_t context = int32_t(spec->prompt_rows + generated - 1);
+    uint32_t pending = 0;
+    EI_CUDA(cudaMemcpyAsync(t.host_tokens, spec->tokens + context, sizeof(uint32_t), cudaMemcpyDeviceToHost, t.stream));
+    synchronize(t);
+    pending = t.host_tokens[0];
+    for (ei_session* s : {&t, &d}) {
+      EI_CUDA(cudaMemcpyAsync(&s->control->context, &context, sizeof(context), cudaMemcpyHostToDevice, s->stream));
+      EI_CUDA(cudaMemcpyAsync(&s->control->pending, &pending, sizeof(pending), cudaMemcpyHostToDevice, s->stream));
+      synchronize(*s);
+      s->context = size_t(context);
+    }
+    spec->bound = size_t(context);
+  });
 }
 
 ei_status ei_session_inject_failure(ei_session* session, int nth_launch, int completion) {

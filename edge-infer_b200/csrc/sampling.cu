@@ -83,7 +83,8 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(const bf
 // Greedy acceptance (reference runtime/src/speculative_decoder.cpp:214-223): emit chosen[0..m] where m is the
 // number of leading drafts with chosen[i] == inputs[i+1]; commit m+1 rows; the last emitted token is pending.
 __device__ void accept_commit(const uint32_t* chosen, int rows, const uint32_t* step_tokens, Control* control,
-                              int32_t* context_length, uint32_t* pending, ei_verify_result* result) {
+                              int32_t* context_length, uint32_t* pending, ei_verify_result* result,
+                              const TokenSink* sink = nullptr) {
   int emitted = 0;
   for (int i = 0; i < rows; ++i) {
     ++emitted;
@@ -94,6 +95,13 @@ __device__ void accept_commit(const uint32_t* chosen, int rows, const uint32_t* 
   if (control) {
     const bool skipped = (control->status & 1) != 0;  // capacity guard tripped: nothing was written
     if (skipped) emitted = 0;
+    if (sink && sink->tokens) {
+      // Token i of this step is the one after the first context + 1 + i tokens of the sequence.
+      for (int i = 0; i < emitted; ++i) {
+        const long long at = (long long)control->context + 1 + i - sink->base;
+        if (at >= 0 && at < sink->count) sink->tokens[at] = chosen[i];
+      }
+    }
     control->context += emitted;
     if (emitted) control->pending = chosen[emitted - 1];
     control->steps += 1;
@@ -123,7 +131,8 @@ __global__ void accept_kernel(const uint32_t* inputs, const uint32_t* targets, i
 __global__ void __launch_bounds__(512) finalize_kernel(const float* best_value, const int* best_index, int parts,
                                                        int rows, uint32_t* targets, const uint32_t* step_tokens,
                                                        Control* control, int32_t* context_length,
-                                                       uint32_t* pending, ei_verify_result* result) {
+                                                       uint32_t* pending, ei_verify_result* result,
+                                                       const TokenSink* sink) {
   __shared__ uint32_t chosen[16];
   grid_dependency_wait();
   const int row = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,7 +155,14 @@ __global__ void __launch_bounds__(512) finalize_kernel(const float* best_value, 
   }
   __syncthreads();
   if (threadIdx.x != 0 || !step_tokens) return;
-  accept_commit(chosen, rows, step_tokens, control, context_length, pending, result);
+  accept_commit(chosen, rows, step_tokens, control, context_length, pending, result, sink);
+}
+
+__global__ void adopt_control_kernel(Control* mine, const Control* theirs) {
+  if (threadIdx.x || blockIdx.x) return;
+  mine->context = theirs->context;
+  mine->pending = theirs->pending;
+  mine->status |= theirs->status;
 }
 
 }  // namespace
@@ -170,9 +186,14 @@ void launch_accept(const uint32_t* inputs, const uint32_t* targets, int rows, in
 
 void launch_finalize(const float* best_value, const int* best_index, int parts, int rows, uint32_t* targets,
                      const uint32_t* step_tokens, Control* control, int32_t* context_length, uint32_t* pending,
-                     ei_verify_result* result, cudaStream_t stream, bool pdl) {
+                     ei_verify_result* result, cudaStream_t stream, bool pdl, const TokenSink* sink) {
   launch(finalize_kernel, dim3(1), dim3(512), 0, stream, pdl, best_value, best_index, parts, rows, targets,
-         step_tokens, control, context_length, pending, result);
+         step_tokens, control, context_length, pending, result, sink);
+}
+
+void launch_adopt_control(Control* mine, const Control* theirs, cudaStream_t stream) {
+  adopt_control_kernel<<<1, 32, 0, stream>>>(mine, theirs);
+  check_launch();
 }
 
 }  // namespace ei

@@ -287,3 +287,67 @@ class SessionBatch:
         except Exception:
             pass
 
+
+
+class SpeculativeDecoder:
+    """A target and a draft session generating together without host round trips: mirrors the reference's
+    SpeculativeDecoder (runtime/src/speculative_decoder.cpp:227-306), greedy only. A round = k + 1 draft decode
+    steps chained on the device, one verify forward of [pending, d1..dk] on the target, acceptance and commit on the
+    device; the host synchronises only in drain()."""
+
+    def __init__(self, target: "Session", draft: "Session", drafts_per_round: int):
+        self._lib = abi.load_library()
+        self.target, self.draft, self.drafts_per_round = target, draft, int(drafts_per_round)
+        out = C.c_void_p()
+        abi.check(self._lib.ei_speculative_create(target._handle, draft._handle, self.drafts_per_round, C.byref(out)))
+        self._handle = out
+
+    def prefill(self, tokens: Sequence[int]) -> int:
+        """Both sessions take the prompt; returns the first generated token."""
+        ids = np.ascontiguousarray(tokens, dtype=np.uint32)
+        first = C.c_uint32()
+        abi.check(self._lib.ei_speculative_prefill(self._handle, ids.ctypes.data_as(C.c_void_p), ids.size, C.byref(first)))
+        return int(first.value)
+
+    def enqueue(self, rounds: int) -> None:
+        abi.check(self._lib.ei_speculative_enqueue(self._handle, int(rounds)))
+
+    def drain(self, limit: int = 1 << 20) -> List[int]:
+        """Waits; returns every token generated since the prefill (the first token included)."""
+        count = C.c_size_t()
+        abi.check(self._lib.ei_speculative_drain(self._handle, None, 0, C.byref(count), None))
+        room = min(int(count.value), int(limit))
+        out = np.zeros(max(room, 1), dtype=np.uint32)
+        abi.check(self._lib.ei_speculative_drain(self._handle, out.ctypes.data_as(C.c_void_p), room, C.byref(count), None))
+        return [int(t) for t in out[:room]]
+
+    def truncate(self, generated: int) -> None:
+        abi.check(self._lib.ei_speculative_truncate(self._handle, int(generated)))
+
+    def generate(self, tokens: Sequence[int], max_new_tokens: int, eos: Optional[int] = None,
+                 rounds_per_drain: int = 8) -> List[int]:
+        """Greedy generation of up to max_new_tokens tokens after the prompt, stopping after an EOS token."""
+        self.prefill(tokens)
+        out: List[int] = []
+        while True:
+            out = self.drain()
+            if eos is not None and eos in out:
+                out = out[:out.index(eos) + 1]
+                break
+            if len(out) >= max_new_tokens:
+                out = out[:max_new_tokens]
+                break
+            self.enqueue(rounds_per_drain)
+        self.truncate(len(out))
+        return out
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.ei_speculative_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

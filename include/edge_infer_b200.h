@@ -286,6 +286,35 @@ ei_status ei_session_read_logits(ei_session* session, size_t rows, void* host_lo
 /* Kernels launched by this session's last step (the launches inside one captured graph). */
 size_t ei_session_launches_per_step(const ei_session* session, size_t rows);
 
+/* ---- draft + verify loop without host round trips ----------------------------------------------------
+ * ref: SpeculativeDecoder<T>::generate_with_callback (runtime/src/speculative_decoder.cpp:227-306), whose round
+ * is generate_draft_tokens (:176-187, one stream synchronisation per draft token) followed by verify_greedy
+ * (:200-224, device-to-host copies and a host comparison). Here a round is enqueued as a whole: the draft
+ * session decodes drafts_per_round + 1 tokens, each from the token its previous step left on the device, the
+ * target session verifies [pending, d1..dk] in one forward, accepts and commits on the device, and the draft
+ * session adopts the target's context length and pending token (both keep the pending input plus every
+ * accepted one, :219-223). The host synchronises only in ei_speculative_drain. Greedy (top_k = 1) only, as the
+ * reference. Both sessions must live on one device, share the vocabulary and must not be used directly while
+ * the decoder drives them; destroy the decoder before its sessions. */
+typedef struct ei_speculative ei_speculative;
+ei_status ei_speculative_create(ei_session* target, ei_session* draft, size_t drafts_per_round,
+                                ei_speculative** out);
+void ei_speculative_destroy(ei_speculative* spec);
+/* Starts a request: both sessions take the whole prompt; the target's greedy token after it is the first
+ * generated token (*first_token, optional) and the pending token of both sessions. */
+ei_status ei_speculative_prefill(ei_speculative* spec, const uint32_t* host_tokens, size_t rows,
+                                 uint32_t* first_token);
+/* Enqueues `rounds` rounds without synchronising. The host does not know the context length between drains and
+ * bounds it by full acceptance: EI_LENGTH if that bound would pass the capacity (drain, then enqueue less). */
+ei_status ei_speculative_enqueue(ei_speculative* spec, size_t rounds);
+/* Waits for the enqueued rounds. *count = tokens generated since the prefill (the first token included);
+ * host_tokens (optional, room for `capacity`) receives them from the first on; *last = the last verify step. */
+ei_status ei_speculative_drain(ei_speculative* spec, uint32_t* host_tokens, size_t capacity, size_t* count,
+                               ei_verify_result* last);
+/* Keeps the first `generated` generated tokens (1 <= generated <= count): the last kept token becomes pending in
+ * both sessions, the ones before it stay in both caches. ref: EOS truncation, speculative_decoder.cpp:302-304. */
+ei_status ei_speculative_truncate(ei_speculative* spec, size_t generated);
+
 /* Test hook (host-side fault injection, no GPU fault): the N-th next kernel launch of this session
  * fails with EI_RUNTIME before it is submitted (N = 0 disarms); `completion` != 0 makes the next stream
  * completion report failure after a real wait, which poisons the session.

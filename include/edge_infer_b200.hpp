@@ -244,4 +244,33 @@ class Session {
   ei_session* session_ = nullptr;
 };
 
+// The reference's SpeculativeDecoder<T> (runtime/src/speculative_decoder.cpp:227-306) over a target and a draft
+// Session: greedy only; rounds run on the device, the host synchronises in drain().
+class SpeculativeDecoder {
+ public:
+  SpeculativeDecoder(Session& target, Session& draft, std::size_t drafts_per_round) {
+    check(ei_speculative_create(target.native(), draft.native(), drafts_per_round, &decoder_));
+  }
+  ~SpeculativeDecoder() { ei_speculative_destroy(decoder_); }
+  SpeculativeDecoder(const SpeculativeDecoder&) = delete;
+  SpeculativeDecoder& operator=(const SpeculativeDecoder&) = delete;
+
+  std::uint32_t prefill(const std::uint32_t* tokens, std::size_t rows) {
+    std::uint32_t first = 0;
+    check(ei_speculative_prefill(decoder_, tokens, rows, &first));
+    return first;  // the first generated token
+  }
+  void enqueue(std::size_t rounds) { check(ei_speculative_enqueue(decoder_, rounds)); }
+  // Waits; returns how many tokens have been generated since the prefill and copies up to `capacity` of them.
+  std::size_t drain(std::uint32_t* tokens, std::size_t capacity) {
+    std::size_t count = 0;
+    check(ei_speculative_drain(decoder_, tokens, capacity, &count, nullptr));
+    return count;
+  }
+  void truncate(std::size_t generated) { check(ei_speculative_truncate(decoder_, generated)); }
+
+ private:
+  ei_speculative* decoder_ = nullptr;
+};
+
 }  // namespace edge_infer_b200
