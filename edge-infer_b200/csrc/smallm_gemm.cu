@@ -1,5 +1,6 @@
 // Dispatch, planning and fallbacks for the small-M weight-streaming GEMM.
 #include "awq_tma.cuh"
+#include "dense_tma.cuh"
 
 #include <algorithm>
 #include <stdexcept>
@@ -115,6 +116,7 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
     plan.smem_limit = smem_limit;
   }
   if (smem > smem_limit) return plan;
+  plan.smem_limit = smem_limit;
   plan.fast = true;
   plan.ksplit = ks;
   plan.units_per_warp = per_warp;
@@ -149,7 +151,7 @@ void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void
                                                ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (result != CUDA_SUCCESS)
-    throw std::runtime_error(std::string("Tensor map for AWQ ") + what + " could not be encoded: " +
+    throw std::runtime_error(std::string("Tensor map for ") + what + " could not be encoded: " +
                              std::to_string(int(result)));
 }
 
@@ -230,10 +232,50 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
   dispatch_awq(plan.high, pair, cfg.tma_sz != 0, full && cfg.tma_sz != 0, plan.grid, smem, stream, pdl, maps, p, cfg);
 }
 
+// The TMA-fed BF16 kernel takes weights whose rows are 16-byte aligned and K in steps of a warp's 256 inputs.
+bool dense_tma_eligible(const GemmPlan& plan, const GemmParams& p) {
+  if (p.K % kDenseWarpInputs || !aligned_16(p.w) || p.ldw % 8 || !aligned_16(p.x) || p.x_stride % 8) return false;
+  const int parts_total = p.K / kDenseWarpInputs;
+  if ((parts_total + plan.ksplit - 1) / plan.ksplit > kGemmWarps) return false;
+  const DenseLaunch smallest{2, std::min(64, ((parts_total + plan.ksplit - 1) / plan.ksplit) * 4)};
+  return dense_layout(smallest).total <= plan.smem_limit;
+}
+
+void launch_dense_tma(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, bool pdl) {
+  const int parts_total = p.K / kDenseWarpInputs;
+  DenseLaunch cfg{};
+  cfg.units_box = std::min(64, ((parts_total + plan.ksplit - 1) / plan.ksplit) * 4);  // the largest slice
+  cfg.stages = kDenseMaxStages;
+  while (cfg.stages > 2 && dense_layout(cfg).total > plan.smem_limit) --cfg.stages;
+  const size_t smem = dense_layout(cfg).total;
+  CUtensorMap weights{};
+  {
+    // BF16 weights as [unit of 64 inputs][row][64 values]: a box is one tile, staged as [unit][row][128 B].
+    const cuuint64_t dims[3] = {64, cuuint64_t(p.N), cuuint64_t(p.K / 64)};
+    const cuuint64_t strides[2] = {cuuint64_t(p.ldw) * 2, 128};
+    const cuuint32_t box[3] = {64, 8, cuuint32_t(cfg.units_box)};
+    encode_map(&weights, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p.w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+               "dense weights");
+  }
+  static thread_local int configured_device = -1;
+  int device = 0;
+  EI_CUDA(cudaGetDevice(&device));
+  if (configured_device != device) {
+    EI_CUDA(cudaFuncSetAttribute(dense_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    EI_CUDA(cudaFuncSetAttribute(dense_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_device = device;
+  }
+  if (plan.high)
+    launch(dense_tma_kernel<true>, dim3(plan.grid), dim3(kGemmThreads), smem, stream, pdl, weights, p, cfg);
+  else
+    launch(dense_tma_kernel<false>, dim3(plan.grid), dim3(kGemmThreads), smem, stream, pdl, weights, p, cfg);
+}
+
 }  // namespace
 
 void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
   if (awq) return launch_awq(plan, p, stream, pdl);
+  if (dense_tma_eligible(plan, p)) return launch_dense_tma(plan, p, stream, pdl);
   const int U = plan.units_per_warp;
   if (U == 1) return launch_high<1, 6, 6>(plan, p, stream, pdl);
   if (U == 2) return launch_high<2, 4, 4>(plan, p, stream, pdl);
