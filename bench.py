@@ -58,23 +58,57 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: in-process NVML reads every few
+    milliseconds (the region can be shorter than one nvidia-smi start-up), nvidia-smi in a loop if NVML cannot
+    be loaded. Only reads: no setting of the GPU is touched."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, device_index: int):
         self.device_index = device_index
-        self.lines = []
+        self.lines, self.samples = [], []
         self.process = None
+        self.thread = None
+        self.stop_event = threading.Event()
+        self.max_clock = None
+        self.source = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            masks = {"hw_slowdown": pynvml.nvmlClocksEventReasonHwSlowdown,
+                     "hw_thermal_slowdown": pynvml.nvmlClocksEventReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": pynvml.nvmlClocksEventReasonSwThermalSlowdown,
+                     "sw_power_cap": pynvml.nvmlClocksEventReasonSwPowerCap}
+
+            def loop():
+                while not self.stop_event.is_set():
+                    try:
+                        clock = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        bits = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                        self.samples.append((clock, [name for name, mask in masks.items() if bits & mask]))
+                    except pynvml.NVMLError:
+                        pass
+                    self.stop_event.wait(0.005)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            self.source = "nvml"
+            return
+        except Exception:
+            self.thread = None
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            self.source = "nvidia-smi"
         except OSError:
             self.process = None
 
@@ -83,30 +117,36 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        clocks, max_clocks, reasons = [], [], set()
+        if self.thread:
+            self.stop_event.set()
+            self.thread.join(timeout=2)
+            for clock, active in self.samples:
+                clocks.append(clock)
+                reasons.update(active)
+            max_clocks = [self.max_clock] if self.max_clock else []
         if self.process:
             self.process.terminate()
             try:
                 self.process.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.process.kill()
-        clocks, max_clocks, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                clocks.append(float(parts[1]))
-                max_clocks.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, value in zip(names, parts[5:9]):
-                if value.lower().startswith("active"):
-                    reasons.add(name)
+            for line in self.lines:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    clocks.append(float(parts[1]))
+                    max_clocks.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, value in zip(self.NAMES, parts[5:9]):
+                    if value.lower().startswith("active"):
+                        reasons.add(name)
         if not clocks:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "reasons": sorted(reasons),
-                "samples": len(clocks)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": self.source}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks) if max_clocks else None,
+                "reasons": sorted(reasons), "samples": len(clocks), "source": self.source}
 
 
 def cpu_verify_sample(oracle, package, threads: int, repeats: int):
