@@ -61,6 +61,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
 }
 
 __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
+  EI_TIMELINE_SCOPE(kTimelineAttention);
   extern __shared__ __align__(128) unsigned char smem[];
   // The context length was written by the previous step; the preceding kernel of this step only appends the
   // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
@@ -234,6 +235,7 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
 // splits w, w+4, ... and the four partial sums are added in warp order. The order of every addition is
 // fixed, so replays give identical bits.
 __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionParams p) {
+  EI_TIMELINE_SCOPE(kTimelineMerge);
   __shared__ float weights[64];
   __shared__ float warp_values[4];
   __shared__ float4 partial_out[4][32];
@@ -329,3 +331,5 @@ void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool
 }
 
 }  // namespace ei
+
+EI_TIMELINE_EXPORT(attention)

@@ -144,6 +144,7 @@ __host__ __device__ inline AwqLayout awq_layout(const AwqLaunch& cfg) {
 template <bool kHigh, bool kPair, bool kTmaSz, bool kFull>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     awq_tma_kernel(const __grid_constant__ AwqTensorMaps maps, const GemmParams p, const AwqLaunch cfg) {
+  EI_TIMELINE_SCOPE(kTimelineAwqGemm);
   constexpr int kBlock = 136;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_address(smem_raw) & 1023u)) & 1023u);

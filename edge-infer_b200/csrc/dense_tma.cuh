@@ -44,6 +44,7 @@ __host__ __device__ inline DenseLayout dense_layout(const DenseLaunch& cfg) {
 template <bool kHigh>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     dense_tma_kernel(const __grid_constant__ CUtensorMap weights, const GemmParams p, const DenseLaunch cfg) {
+  EI_TIMELINE_SCOPE(kTimelineDenseGemm);
   constexpr int kBlock = 136;
   constexpr int kParts = 4;
   extern __shared__ unsigned char smem_raw[];

@@ -99,6 +99,7 @@ __global__ void store_kv_kernel(const bf16* source, bf16* cache, size_t count, s
 }
 
 __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedParams p) {
+  EI_TIMELINE_SCOPE(kTimelineEmbedNorm);
   __shared__ float shared[32];
   __shared__ uint32_t token_shared;
   grid_dependency_wait();
@@ -152,6 +153,7 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
 // One warp per (row, head); lane l owns rotation pairs 2l and 2l+1, i.e. elements
 // {2l, 2l+1} of the first half and {64+2l, 64+2l+1} of the second.
 __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams p) {
+  EI_TIMELINE_SCOPE(kTimelineQkNormRope);
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int per_row = p.heads + 2 * p.kv_heads;
@@ -262,6 +264,7 @@ __device__ __forceinline__ void store4_bf16(bf16* p, float4 v) {
 // kRowGroups: groups of 4096 values a row needs (1 for hidden <= 4096), so that small rows keep few registers.
 template <int kRowGroups>
 __global__ void __launch_bounds__(kRowThreads) residual_norm_vec_kernel(const ResidualNormParams p) {
+  EI_TIMELINE_SCOPE(kTimelineResidualNorm);
   __shared__ float shared[32];
   const int row = blockIdx.x;
   bf16* residual = p.residual + size_t(row) * p.hidden;
@@ -396,3 +399,5 @@ void launch_residual_norm(const ResidualNormParams& p, cudaStream_t stream, bool
 }
 
 }  // namespace ei
+
+EI_TIMELINE_EXPORT(elementwise)

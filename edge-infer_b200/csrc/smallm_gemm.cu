@@ -284,3 +284,5 @@ void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream
 }
 
 }  // namespace ei
+
+EI_TIMELINE_EXPORT(smallm_gemm)
