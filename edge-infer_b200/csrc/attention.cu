@@ -239,12 +239,14 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   __shared__ float weights[64];
   __shared__ float warp_values[4];
   __shared__ float4 partial_out[4][32];
+  // The context length was written by the previous step (or by the host): it does not come from the kernel
+  // this one waits for, so it is read first and the wait hides its latency.
+  const int offset = p.device_offset ? *p.device_offset : p.host_offset;
   grid_dependency_wait();
   grid_launch_dependents();
   const int slot = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = p.rows * p.heads;
-  const int offset = p.device_offset ? *p.device_offset : p.host_offset;
   const int length = offset + p.rows;
   if (offset < 0 || length > p.capacity) return;
   const int splits = min(64, (length + p.chunk - 1) / p.chunk);
