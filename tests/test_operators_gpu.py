@@ -175,7 +175,10 @@ def test_awq_gate_up_silu_matches_unfused_sequence(cuda, package, oracle, ctx, r
 
 
 @pytest.mark.parametrize("rows", [1, 5, 16, 21])
-@pytest.mark.parametrize("nk", [(4096, 2048), (151936, 1024), (1000, 320), (6144, 4096)])
+# K = 6144 and 12288 take two and three K slices (FP32 partials + the fixed-order merge), K = 768 leaves most
+# warps of the TMA-fed kernel without inputs, K = 320 takes the register-prefetching kernel.
+@pytest.mark.parametrize("nk", [(4096, 2048), (151936, 1024), (1000, 320), (6144, 4096), (2048, 6144), (1024, 12288),
+                                (512, 768)])
 def test_dense_linear(cuda, package, oracle, ctx, rows, nk):
     torch, ops, syn = cuda, package.operators, package.synthetic
     n, k = nk
