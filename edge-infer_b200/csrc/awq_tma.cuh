@@ -244,7 +244,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
   }
+  // Barriers initialised, up-front scales / zeros visible: the block synchronises here, while it would wait for
+  // its predecessor anyway, so that nothing after the activation loads below needs a block-wide barrier.
+  __syncthreads();
   grid_dependency_wait();
+  grid_launch_dependents();
 
   // A fragments of this warp's 256 inputs, pinned in registers.
   const bool live = kFull || warp < units;
@@ -260,8 +264,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   asm volatile("" ::: "memory");  // the activation loads are issued before the rest of the ring is requested
   if (threadIdx.x == 0)
     for (int ph = kAwqEarlyPhases; ph < ring_phases; ++ph) issue(ph);
-  __syncthreads();  // barriers initialised; up-front scales / zeros visible
-  grid_launch_dependents();
   if (kTmaSz && !mbarrier_wait(sz_full, 0)) {
     if (p.status) atomicOr(p.status, 4);
     return;  // the whole block sees the same incomplete phase

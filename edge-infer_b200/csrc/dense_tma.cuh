@@ -84,7 +84,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     issue(0);  // weights do not depend on the preceding kernel; more now would delay the activation loads below
   }
+  __syncthreads();  // barriers initialised: synchronise while the block would wait for its predecessor anyway
   grid_dependency_wait();
+  grid_launch_dependents();
 
   // A fragments of this warp's 256 inputs: cell (unit u, half h) of lane (g, c) holds inputs
   // [64 u + 32 h + 8 c, + 8) of rows g and g + 8: the four lanes of a row read 64 contiguous bytes per load.
@@ -104,8 +106,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   asm volatile("" ::: "memory");  // the activation loads are issued before the rest of the ring is requested
   if (threadIdx.x == 0)
     for (int s = 1; s < cfg.stages; ++s) issue(s);
-  __syncthreads();  // barriers initialised
-  grid_launch_dependents();
 
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
   const int e = warp * 8 + (lane & 7);
