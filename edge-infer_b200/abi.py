@@ -150,6 +150,7 @@ PROTOTYPES = {
     "ei_session_read_logits": (_S, [_P, _Z, _P]),
     "ei_session_launches_per_step": (_Z, [_P, _Z]),
     "ei_session_inject_failure": (_S, [_P, C.c_int, C.c_int]),
+    "ei_session_inject_wait_timeout": (_S, [_P, C.c_uint32]),
 }
 
 _lib = None

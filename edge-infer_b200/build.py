@@ -2,7 +2,6 @@
 
     python edge-infer_b200/build.py            # incremental
     python edge-infer_b200/build.py --force
-    python edge-infer_b200/build.py --timeline   # second library whose kernels record a timeline (timeline.py)
 
 Output: edge-infer_b200/libedge_infer_b200.so (git-ignored; it travels with the tree).
 """
@@ -30,32 +29,6 @@ FLAGS = [
 def _newest_dependency() -> float:
     paths = list(CSRC.glob("*")) + [HERE.parent / "include" / "edge_infer_b200.h", Path(__file__)]
     return max(p.stat().st_mtime for p in paths)
-
-
-TIMELINE_LIB = HERE / "libedge_infer_b200_timeline.so"
-
-
-def build_timeline() -> Path:
-    """The same sources with -DEI_TIMELINE: every block of the step's kernels records start / wait / end times."""
-    objects = []
-    out_dir = OBJ / "timeline"
-    out_dir.mkdir(parents=True, exist_ok=True)
-
-    def one(source: str) -> str:
-        out = out_dir / (source + ".o")
-        result = subprocess.run([NVCC, *FLAGS, "-DEI_TIMELINE", "-c", str(CSRC / source), "-o", str(out)],
-                                capture_output=True, text=True)
-        if result.returncode:
-            raise RuntimeError(f"nvcc failed for {source}:\n{result.stdout}\n{result.stderr}")
-        return str(out)
-
-    with ThreadPoolExecutor(max_workers=8) as pool:
-        objects = list(pool.map(one, SOURCES))
-    result = subprocess.run([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(TIMELINE_LIB),
-                             *objects, "-lcudart"], capture_output=True, text=True)
-    if result.returncode:
-        raise RuntimeError(f"link failed:\n{result.stdout}\n{result.stderr}")
-    return TIMELINE_LIB
 
 
 def _compile(source: str, verbose: bool) -> None:
@@ -90,8 +63,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    if "--timeline" in sys.argv:
-        print(build_timeline())
-        sys.exit(0)
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)

@@ -421,8 +421,7 @@ static void run_attention(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view
   p.capacity = int(k.shape[0]);
   p.device_offset = device_offset;
   p.host_offset = int(offset);
-  p.chunk = attention_chunk_for(length);
-  p.max_splits = int((length + p.chunk - 1) / p.chunk);
+  p.max_splits = attention_grid_splits(length, p.kv_heads, ctx->multiprocessors);
   p.scratch = static_cast<float*>(scratch);
   p.out = static_cast<bf16*>(out.data);
   p.out_stride = int(out.stride[0]);
@@ -476,6 +475,12 @@ static void* static_attention_scratch_address() {
 ei_status ei_attention_prefill_static_bf16(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view3 v, ei_view3 out,
                                            size_t offset) {
   return guarded([&] {
+    // The array is resolved for the CURRENT device: a context prepared on another one would be served the
+    // wrong device's array.
+    int current = -1;
+    EI_CUDA(cudaGetDevice(&current));
+    if (!ctx || ctx->device != current)
+      throw std::invalid_argument("The execution context belongs to another CUDA device than the current one");
     const size_t length = offset + q.shape[0];
     const size_t needed = attention_scratch_bytes(q.shape[0], q.shape[1], length);
     if (needed > kStaticAttentionScratchBytes)

@@ -2,14 +2,13 @@
 //
 // A tile is 8 output features = 8 consecutive rows of the N-major packed weight matrix, over one K slice of
 // up to 4096 inputs. One thread brings a whole tile into shared memory with a single tiled TMA copy
-// (cp.async.bulk.tensor) that completes on an mbarrier; a ring of tiles is always in flight per block, so HBM
-// streams continuously, independently of the warps' register scoreboards, and the loop issues no global loads
-// at all. The group scales and packed zero points of all rows the block will touch come in up front, by one
+// (cp.async.bulk.tensor) that completes on an mbarrier; a ring of tiles is always in flight per block, so HBM streams continuously, independently of
+// the warps' register scoreboards, and the loop issues no global loads at all. The group scales and packed zero points of all rows the block will touch come in up front, by one
 // box each (a TMA copy costs about 100 ns of the copy engine's time whatever its size, so few large copies).
 //
 // The weight matrix is described to TMA as a rank-3 tensor [unit of 256 inputs][row][128 bytes], so that the
 // staged tile is [unit][row][128 B] and the 128-byte swizzle places the 16-byte chunk j of row r at chunk
-// (j ^ r): the eight rows a quarter-warp reads in one 128-bit load then fall into eight distinct bank groups.
+// (j ^ r): the eight rows a quarter-warp reads in one load then fall into eight distinct bank groups.
 //
 // The <= 16 activation rows never change while the block runs and warp w always works on inputs
 // [256 w, 256 w + 256) of the block's K slice, so its A fragments are loaded once, in the register order
@@ -22,8 +21,10 @@
 // fetched once, with ordinary loads, for every tile the block will touch, before the kernel waits for its
 // predecessor.
 //
-// Every wait on an mbarrier is bounded: if a copy does not complete within the limit the block records the
-// failure in GemmParams::status and leaves without touching its outputs again.
+// Every wait on an mbarrier is bounded, and the decision is the block's, not a thread's: a thread whose wait
+// ran out raises a shared flag that all threads read after the phase's block-wide barrier, so either all go on or all record the failure in
+// GemmParams::status, wait (bounded again) for the copies still in flight and leave without touching the
+// outputs again.
 #pragma once
 
 #include <cuda.h>
@@ -37,7 +38,7 @@ constexpr int kAwqSliceUnits = 16;            // 256-input units per K slice: on
 constexpr uint32_t kAwqWaitLimit = 1u << 22;  // polls of ~100 ns before a wait gives up
 
 struct AwqTensorMaps {
-  CUtensorMap weights;  // u64 [units][N][16], box [units_box][8][16], 128-byte swizzle
+  CUtensorMap weights;  // u32 [units][N][32], box [units_box][8][32], 128-byte swizzle
   CUtensorMap scales;   // bf16 [N][padded_groups], box [8][scale_box]
   CUtensorMap zeros;    // i32 [N][zero_stride], box [8][zero_box]
 };
@@ -51,6 +52,9 @@ struct AwqLaunch {
   int zero_box;         // words per staged zero row
   int sz_boxes;         // TMA boxes of scale / zero rows per block: 1, or 2 in pair mode (gate rows, up rows)
   int sz_rows;          // rows per such box (<= 256)
+  uint32_t wait_limit;  // polls before a wait gives up (0: kAwqWaitLimit)
+  uint32_t extra_tx;    // test hook: bytes added to what the first weight copy is expected to deliver, so that
+                        // its barrier never completes and the bounded waits run out (0 in production)
 };
 
 __device__ __forceinline__ uint32_t smem_address(const void* p) {
@@ -88,9 +92,9 @@ __device__ __forceinline__ bool mbarrier_test_wait(uint64_t* bar, uint32_t parit
 // Bounded wait; false if the phase did not complete within the limit. The non-blocking test comes first: a
 // try_wait with a time hint costs a few hundred cycles even when the phase has long completed, which is the
 // normal case here (the ring runs ahead of the arithmetic).
-__device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kAwqWaitLimit) {
   if (mbarrier_test_wait(bar, parity)) return true;
-  for (uint32_t polls = 0; polls < kAwqWaitLimit; ++polls)
+  for (uint32_t polls = 0; polls < limit; ++polls)
     if (mbarrier_try_wait(bar, parity)) return true;
   return false;
 }
@@ -144,7 +148,6 @@ __host__ __device__ inline AwqLayout awq_layout(const AwqLaunch& cfg) {
 template <bool kHigh, bool kPair, bool kTmaSz, bool kFull>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     awq_tma_kernel(const __grid_constant__ AwqTensorMaps maps, const GemmParams p, const AwqLaunch cfg) {
-  EI_TIMELINE_SCOPE(kTimelineAwqGemm);
   constexpr int kBlock = 136;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_address(smem_raw) & 1023u)) & 1023u);
@@ -169,24 +172,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   float* part = reinterpret_cast<float*>(smem + layout.part_offset);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + layout.barrier_offset);
   uint64_t* sz_full = full + kAwqMaxStages;
+  volatile int* failed = reinterpret_cast<volatile int*>(sz_full + 1);  // set by a thread whose wait ran out
   unsigned char* sz = smem + layout.sz_offset;
   const int scale_pitch = cfg.scale_box * 2, zero_pitch = cfg.zero_box * 4;
 
   // One thread brings in the two tiles of a phase, one copy each, on one barrier (a wait costs a few hundred
-  // cycles even when the data has long arrived, so there is one per phase, not one per tile).
+  // cycles even when the data has long arrived, so there is one per phase, not one per tile). One copy for
+  // both tiles (a 16-row box, or a rank-4 box over the gate and the up half) was measured slower to deliver.
   const int ring_phases = cfg.stages / kAwqPhaseTiles;
+  const int phase_bytes = kAwqPhaseTiles * layout.weight_bytes;
+  const uint32_t wait_limit = cfg.wait_limit ? cfg.wait_limit : kAwqWaitLimit;
   auto issue = [&](int phase) {
     const int index = phase * kAwqPhaseTiles;
     if (index >= item_count) return;
     const int slot = phase % ring_phases, tiles_here = min(kAwqPhaseTiles, item_count - index);
-    mbarrier_expect_tx(&full[slot], uint32_t(tiles_here * layout.weight_bytes));
+    mbarrier_expect_tx(&full[slot], uint32_t(tiles_here * layout.weight_bytes) + (phase == 0 ? cfg.extra_tx : 0u));
     for (int t = 0; t < tiles_here; ++t)
-      tma_load_3d(stages + size_t(slot * kAwqPhaseTiles + t) * layout.weight_bytes, &maps.weights, 0,
+      tma_load_3d(stages + size_t(slot) * phase_bytes + size_t(t) * layout.weight_bytes, &maps.weights, 0,
                   tile_of(item_begin + index + t) * 8, unit_begin, &full[slot]);
   };
   if (threadIdx.x == 0) {
     for (int s = 0; s < ring_phases; ++s) mbarrier_init(&full[s], 1);
     mbarrier_init(sz_full, 1);
+    *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (kTmaSz) {
@@ -262,12 +270,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       load_cell<kHigh>(frag[cell], p.x, p.x_stride, live ? p.M : 0, g, k + cell * 32);
   }
   asm volatile("" ::: "memory");  // the activation loads are issued before the rest of the ring is requested
+  // One thread requests the phases one after another: they then arrive in the order they are needed. Requested
+  // side by side by several warps (measured), their bytes interleave and the first phase lands microseconds late.
   if (threadIdx.x == 0)
     for (int ph = kAwqEarlyPhases; ph < ring_phases; ++ph) issue(ph);
-  if (kTmaSz && !mbarrier_wait(sz_full, 0)) {
-    if (p.status) atomicOr(p.status, 4);
-    return;  // the whole block sees the same incomplete phase
-  }
+  bool sz_ok = true;
+  if (kTmaSz) sz_ok = mbarrier_wait(sz_full, 0, wait_limit);
 
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
   const int e = warp * 8 + (lane & 7);
@@ -400,11 +408,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   int pending = -1;  // phase whose partials sit in `loaded`
   int slot = 0;          // ring position of the current phase
   uint32_t parity = 0;   // of the current pass over the ring
-  for (int index = 0, step = 0; index < item_count; index += kAwqPhaseTiles, ++step) {
+  int gave_up = 0, steps_done = 0;
+  for (int index = 0, step = 0; index < item_count && !gave_up; index += kAwqPhaseTiles, ++step) {
     const int phase = step & 1;
     float acc[kAwqPhaseTiles][4];
-    const bool ok = mbarrier_wait(&full[slot], parity);
-    const uint32_t tile_address = stages_address + uint32_t(slot * kAwqPhaseTiles) * layout.weight_bytes;
+    const bool ok = sz_ok && mbarrier_wait(&full[slot], parity, wait_limit);
+    const uint32_t tile_address = stages_address + uint32_t(slot) * uint32_t(phase_bytes);
     if (ok) compute_tile(tile_address, step, 0, acc[0]);
     if (ok && pending >= 0) finish(pending, loaded);
     if (ok && (kPair || index + 1 < item_count))  // pairs come whole
@@ -415,14 +424,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       slot = 0;
       parity ^= 1;
     }
-    if (!ok) {
-      if (p.status) atomicOr(p.status, 4);
-      return;  // every thread of the block sees the same incomplete phase and leaves here
-    }
     float* mine = part + (size_t(phase) * kAwqPhaseTiles * kGemmWarps + warp) * kBlock + lane * 4;
+    if (ok) {
 #pragma unroll
-    for (int t = 0; t < kAwqPhaseTiles; ++t)
-      *reinterpret_cast<float4*>(mine + size_t(t) * kGemmWarps * kBlock) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+      for (int t = 0; t < kAwqPhaseTiles; ++t)
+        *reinterpret_cast<float4*>(mine + size_t(t) * kGemmWarps * kBlock) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    }
+    // The decision to give up is the block's: a thread whose wait ran out raises the flag before the phase's
+    // block-wide barrier and every thread reads it after (below, with the partials, and acts on it at the top of
+    // the next phase, so the read costs the phase nothing).
+    if (!ok) *failed = 1;
     __syncthreads();
     // Every warp has finished reading these stages: refill them with the tiles `stages` ahead.
     if (threadIdx.x == 0) issue(step + ring_phases);  // lands in the slot this phase has just left
@@ -432,7 +443,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
       for (int w = 0; w < 4; ++w) loaded[t][w] = src[size_t(w) * 4 * kBlock];
     }
+    gave_up = *failed;
     pending = step;
+    steps_done = step + 1;
+  }
+  if (gave_up) {
+    if (threadIdx.x == 0) {
+      if (p.status) atomicOr(p.status, 4);
+      // A block never leaves while a copy into its shared memory may be in flight: give every phase still in
+      // the ring its chance to land (bounded again).
+      for (int back = max(0, steps_done - 1); back < steps_done - 1 + ring_phases; ++back)
+        if (back * kAwqPhaseTiles < item_count)
+          mbarrier_wait(&full[back % ring_phases], uint32_t((back / ring_phases) & 1), wait_limit);
+    }
+    __syncthreads();
+    return;
   }
   if (pending >= 0) {
     finish(pending, loaded);

@@ -85,82 +85,9 @@ __device__ __forceinline__ void mma_bf16_16816_first(float (&d)[4], uint32_t a0,
 
 // Programmatic dependent launch: wait until the kernels this one depends on have
 // completed and flushed (no-op when launched without the attribute).
-#ifdef EI_TIMELINE
-// Optional build (-DEI_TIMELINE, edge-infer_b200/build.py --timeline): thread 0 of every block of the step's
-// kernels records when the block started, when its dependency wait returned and when it ended (global timer,
-// nanoseconds), so that the timeline of a step replayed from its CUDA graph can be read back
-// (edge-infer_b200/timeline.py). Each translation unit has its own record buffer.
-struct TimelineRecord {
-  unsigned long long start, waited, end;
-  int kernel, block;
-};
-constexpr unsigned kTimelineCapacity = 1u << 16;
-static __device__ TimelineRecord timeline_records[kTimelineCapacity];
-static __device__ unsigned timeline_count;
-__device__ __forceinline__ unsigned long long timeline_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-struct TimelineScope {
-  unsigned long long start, released;
-  int kernel;
-  __device__ __forceinline__ explicit TimelineScope(int id) : start(0), released(0), kernel(id) {
-    if (threadIdx.x == 0) start = timeline_now();
-  }
-  __device__ __forceinline__ void waited() {
-    if (threadIdx.x == 0) released = timeline_now();
-  }
-  __device__ __forceinline__ ~TimelineScope() {
-    if (threadIdx.x == 0) {
-      const unsigned slot = atomicAdd(&timeline_count, 1u);
-      const int block = int(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-      if (slot < kTimelineCapacity)
-        timeline_records[slot] = TimelineRecord{start, released, timeline_now(), kernel, block};
-    }
-  }
-};
-// Kernels that are not recorded find this object when they wait for their predecessor.
-struct TimelineNone {
-  __device__ __forceinline__ void waited() const {}
-};
-static __device__ const TimelineNone timeline_scope{};
-#define EI_TIMELINE_SCOPE(id) TimelineScope timeline_scope(id)
-// Defines the C entry that reads (or, with reset != 0, clears) this translation unit's records.
-#define EI_TIMELINE_EXPORT(unit)                                                                            \
-  extern "C" int ei_timeline_##unit(void* host, unsigned* count, int reset) {                                \
-    if (reset) {                                                                                            \
-      const unsigned zero = 0;                                                                              \
-      return int(cudaMemcpyToSymbol(ei::timeline_count, &zero, sizeof(zero)));                              \
-    }                                                                                                       \
-    cudaMemcpyFromSymbol(count, ei::timeline_count, sizeof(unsigned));                                      \
-    return int(cudaMemcpyFromSymbol(host, ei::timeline_records, sizeof(ei::TimelineRecord) * ei::kTimelineCapacity)); \
-  }
-#else
-#define EI_TIMELINE_SCOPE(id)
-#define EI_TIMELINE_EXPORT(unit)
-#endif
-// Kernel numbers in timeline records.
-enum TimelineKernel {
-  kTimelineEmbedNorm = 1, kTimelineAwqGemm = 2, kTimelineQkNormRope = 3, kTimelineAttention = 4, kTimelineMerge = 5,
-  kTimelineResidualNorm = 6, kTimelineDenseGemm = 7, kTimelineFinalize = 8
-};
-
-#ifdef EI_TIMELINE
-__device__ __forceinline__ void grid_dependency_wait_raw() {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-// A recorded kernel has a local `timeline_scope` that hides the empty one above.
-#define grid_dependency_wait()    \
-  do {                            \
-    grid_dependency_wait_raw();   \
-    timeline_scope.waited();      \
-  } while (0)
-#else
 __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
-#endif
 // Allow the dependent kernel to begin launching (its own wait still orders data).
 // Rule kept by every kernel of this library: trigger only after the kernel's own grid_dependency_wait().
 // Then, whenever the code a successor runs before ITS wait executes, everything up to this kernel's

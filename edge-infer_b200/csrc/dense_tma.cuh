@@ -23,8 +23,10 @@ constexpr int kDenseMaxStages = 8;
 constexpr int kDenseWarpInputs = 256;  // inputs of the slice one warp owns: four 64-input units
 
 struct DenseLaunch {
-  int stages;     // tiles in flight per block
-  int units_box;  // 64-input units the weight box covers (<= 64)
+  int stages;           // tiles in flight per block
+  int units_box;        // 64-input units the weight box covers (<= 64)
+  uint32_t wait_limit;  // polls before a wait gives up (0: kAwqWaitLimit)
+  uint32_t extra_tx;    // test hook: bytes the first copy is expected to deliver beyond what it does (0 in production)
 };
 
 struct DenseLayout {
@@ -44,7 +46,6 @@ __host__ __device__ inline DenseLayout dense_layout(const DenseLaunch& cfg) {
 template <bool kHigh>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     dense_tma_kernel(const __grid_constant__ CUtensorMap weights, const GemmParams p, const DenseLaunch cfg) {
-  EI_TIMELINE_SCOPE(kTimelineDenseGemm);
   constexpr int kBlock = 136;
   constexpr int kParts = 4;
   extern __shared__ unsigned char smem_raw[];
@@ -70,16 +71,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   unsigned char* stages = smem + layout.stage_offset;
   float* part = reinterpret_cast<float*>(smem + layout.part_offset);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + layout.barrier_offset);
+  volatile int* failed = reinterpret_cast<volatile int*>(full + kDenseMaxStages);  // set by a thread whose wait ran out
+  const uint32_t wait_limit = cfg.wait_limit ? cfg.wait_limit : kAwqWaitLimit;
 
   auto issue = [&](int index) {
     if (index >= item_count) return;
     const int slot = index % cfg.stages;
-    mbarrier_expect_tx(&full[slot], uint32_t(layout.tile_bytes));
+    mbarrier_expect_tx(&full[slot], uint32_t(layout.tile_bytes) + (index == 0 ? cfg.extra_tx : 0u));
     tma_load_3d(stages + size_t(slot) * layout.tile_bytes, &weights, 0, tile_of(item_begin + index) * 8,
                 part_begin * 4, &full[slot]);
   };
   if (threadIdx.x == 0) {
     for (int s = 0; s < cfg.stages; ++s) mbarrier_init(&full[s], 1);
+    *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     issue(0);  // weights do not depend on the preceding kernel; more now would delay the activation loads below
@@ -130,15 +134,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   int slot = 0;
   uint32_t parity = 0;
-  for (int index = 0; index < item_count; ++index) {
+  // Giving up is the block's decision: a thread whose wait ran out raises the flag before the tile's block-wide
+  // barrier; every thread reads it after the barrier and acts on it at the top of the next tile.
+  int gave_up = 0, tiles_done = 0;
+  for (int index = 0; index < item_count && !gave_up; ++index) {
     const int item = item_begin + index;
-    const bool ok = mbarrier_wait(&full[slot], parity);
-    if (!ok) {
-      if (p.status) atomicOr(p.status, 4);
-      return;  // every thread of the block sees the same incomplete phase and leaves here
-    }
+    const bool ok = mbarrier_wait(&full[slot], parity, wait_limit);
+    if (!ok) *failed = 1;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, other[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (live) {
+    if (live && ok) {
       const uint32_t tile_address = stages_address + uint32_t(slot) * uint32_t(layout.tile_bytes) + lane_base;
       uint4 w[8];
 #pragma unroll
@@ -165,6 +169,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     // Every warp has finished reading this stage: refill it with the tile `stages` ahead.
     if (threadIdx.x == 0) issue(index + cfg.stages);
+    gave_up = *failed;
+    tiles_done = index + 1;
 
     // Fixed-order reduction by all 16 warps: part q adds the partials of warps q, q + 4, q + 8, q + 12 in that
     // order and the parts are combined by two shuffles, so an output sees the same additions in every run.
@@ -207,6 +213,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
     }
+  }
+
+  if (gave_up) {
+    if (threadIdx.x == 0) {
+      if (p.status) atomicOr(p.status, 4);
+      // A block never leaves while a copy into its shared memory may be in flight: give every tile still in
+      // the ring its chance to land (bounded again).
+      for (int back = max(0, tiles_done - 1); back < min(item_count, tiles_done - 1 + cfg.stages); ++back)
+        mbarrier_wait(&full[back % cfg.stages], uint32_t((back / cfg.stages) & 1), wait_limit);
+    }
+    __syncthreads();
+    return;
   }
 
   if (p.epilogue == kEpiArgmax) {

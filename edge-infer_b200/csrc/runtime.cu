@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(512) residual_norm_bf16_kernel(const bf16* pro
   __syncthreads();
   float total = 0.0f;
   for (int w = 0; w < int(blockDim.x >> 5); ++w) total += shared[w];
-  const float inv = rsqrtf(total / float(hidden) + eps);
+  const float inv = rsqrtf(__fdividef(total, float(hidden)) + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
     normed[size_t(row) * hidden + i] = __float2bfloat16_rn(
         round_bf16(__bfloat162float(residual[size_t(row) * hidden + i]) * inv) * __bfloat162float(norm_weight[i]));
@@ -271,11 +271,14 @@ struct ei_session {
   uint32_t* host_tokens = nullptr;
   Control* host_control = nullptr;
   // plans
-  int attention_chunk = 64, attention_splits = 1;
+  int attention_splits = 1;  // blocks per KV head the attention kernel is launched with
   // state
   size_t context = 0;
+  size_t bound = 0;  // upper bound of the context length after every step enqueued so far (full acceptance)
   bool history_ready = false, poisoned = false;
   int inject_launch = 0, inject_completion = 0;
+  uint32_t inject_wait_polls = 0;  // test hook: the next weight-streaming GEMM gets this poll limit and a copy
+                                   // expectation it cannot meet, so that its bounded waits run out
   size_t launches = 0, launches_per_step[kMaxRows + 1] = {};
   // graphs: [kind][rows]; kind 0 verify (host tokens), 1 verify (device drafts), 2 decode (commit all)
   cudaGraphExec_t graphs[3][kMaxRows + 1] = {};
@@ -348,6 +351,7 @@ void drain_failed(ei_session& s) noexcept {
     return;
   }
   s.context = 0;
+  s.bound = 0;
   s.history_ready = false;
 }
 
@@ -383,6 +387,11 @@ void run_linear(ei_session& s, const PreparedLinear& w, const bf16* x, int rows,
   p.best_value = s.best_value;
   p.best_index = s.best_index;
   p.status = &s.control->status;
+  if (s.inject_wait_polls) {
+    p.wait_limit = s.inject_wait_polls;
+    p.fault_tx = 16;
+    s.inject_wait_polls = 0;  // one launch only
+  }
   tick(s);
   launch_gemm(plan, w.quantized, p, s.stream, pdl);
   if (ksplit_out) *ksplit_out = plan.ksplit;
@@ -467,40 +476,33 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
       run_linear(s, L.qkv, s.normed, rows, kEpiStore, s.qkv, qkv_width, pdl);
     else
       run_generic(s, L.qkv, s.normed, rows, s.qkv, pdl);
-    QkvParams q{};
-    q.qkv = s.qkv;
-    q.rows = rows;
-    q.heads = heads;
-    q.kv_heads = kv_heads;
-    q.qkv_stride = qkv_width;
-    q.q_norm = c.qk_norm ? L.q_norm : nullptr;
-    q.k_norm = c.qk_norm ? L.k_norm : nullptr;
-    q.eps = c.rms_norm_eps;
-    q.rope_table = m.rope_table;
-    q.max_positions = int(c.max_position_embeddings);
-    q.control = s.control;
-    q.capacity = int(s.capacity);
-    q.k_cache = s.k_cache + layer * s.capacity * kv_width;
-    q.v_cache = s.v_cache + layer * s.capacity * kv_width;
-    tick(s);
-    launch_qk_norm_rope_store(q, s.stream, pdl);
-
+    // q|k|v leave the projection raw: the attention kernel normalises and rotates q and k itself and appends
+    // the step's K/V rows (decoder.hpp:122-147 of the reference, in one launch).
     AttentionParams a{};
     a.q = s.qkv;
     a.q_stride = qkv_width;
-    a.k = q.k_cache;
-    a.v = q.v_cache;
+    a.k = s.k_cache + layer * s.capacity * kv_width;
+    a.v = s.v_cache + layer * s.capacity * kv_width;
     a.kv_stride = kv_width;
     a.rows = rows;
     a.heads = heads;
     a.kv_heads = kv_heads;
     a.capacity = int(s.capacity);
     a.device_offset = &s.control->context;
-    a.chunk = s.attention_chunk;
     a.max_splits = s.attention_splits;
     a.scratch = s.attention_scratch;
     a.out = s.attention;
     a.out_stride = heads * 128;
+    a.k_new = s.qkv + heads * 128;
+    a.v_new = s.qkv + (heads + kv_heads) * 128;
+    a.new_stride = qkv_width;
+    a.k_store = s.k_cache + layer * s.capacity * kv_width;
+    a.v_store = s.v_cache + layer * s.capacity * kv_width;
+    a.q_norm = c.qk_norm ? L.q_norm : nullptr;
+    a.k_norm = c.qk_norm ? L.k_norm : nullptr;
+    a.eps = c.rms_norm_eps;
+    a.rope_table = m.rope_table;
+    a.max_positions = int(c.max_position_embeddings);
     tick(s);
     tick(s);
     launch_verify_attention(a, s.stream, pdl);
@@ -552,7 +554,7 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
 
 // Runs a step either eagerly or by replaying its graph (captured on first use after an eager warm run).
 void submit_step(ei_session& s, int rows, StepKind kind) {
-  if (!s.use_graph || kind == kCommitAllNoHead) {
+  if (!s.use_graph || kind == kCommitAllNoHead || s.inject_wait_polls) {
     enqueue_step(s, rows, kind, nullptr);
     return;
   }
@@ -621,26 +623,6 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
       run_generic(lead, L.qkv, lead.normed, total, lead.qkv, pdl);
     for (int j = 0; j < count; ++j) {
       ei_session& s = *batch.sessions[j];
-      QkvParams q{};
-      q.qkv = lead.qkv + size_t(j) * rows * qkv_width;
-      q.rows = rows;
-      q.heads = heads;
-      q.kv_heads = kv_heads;
-      q.qkv_stride = qkv_width;
-      q.q_norm = c.qk_norm ? L.q_norm : nullptr;
-      q.k_norm = c.qk_norm ? L.k_norm : nullptr;
-      q.eps = c.rms_norm_eps;
-      q.rope_table = m.rope_table;
-      q.max_positions = int(c.max_position_embeddings);
-      q.control = s.control;
-      q.capacity = int(s.capacity);
-      q.k_cache = s.k_cache + layer * s.capacity * kv_width;
-      q.v_cache = s.v_cache + layer * s.capacity * kv_width;
-      tick(lead);
-      launch_qk_norm_rope_store(q, lead.stream, pdl);
-    }
-    for (int j = 0; j < count; ++j) {
-      ei_session& s = *batch.sessions[j];
       AttentionParams a{};
       a.q = lead.qkv + size_t(j) * rows * qkv_width;
       a.q_stride = qkv_width;
@@ -652,11 +634,20 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
       a.kv_heads = kv_heads;
       a.capacity = int(s.capacity);
       a.device_offset = &s.control->context;
-      a.chunk = s.attention_chunk;
       a.max_splits = s.attention_splits;
       a.scratch = lead.attention_scratch + size_t(j) * scratch_floats;
       a.out = lead.attention + size_t(j) * rows * heads * 128;
       a.out_stride = heads * 128;
+      a.k_new = a.q + heads * 128;
+      a.v_new = a.q + (heads + kv_heads) * 128;
+      a.new_stride = qkv_width;
+      a.k_store = s.k_cache + layer * s.capacity * kv_width;
+      a.v_store = s.v_cache + layer * s.capacity * kv_width;
+      a.q_norm = c.qk_norm ? L.q_norm : nullptr;
+      a.k_norm = c.qk_norm ? L.k_norm : nullptr;
+      a.eps = c.rms_norm_eps;
+      a.rope_table = m.rope_table;
+      a.max_positions = int(c.max_position_embeddings);
       tick(lead);
       tick(lead);
       launch_verify_attention(a, lead.stream, pdl);
@@ -727,18 +718,25 @@ void read_control(ei_session& s) {
   EI_CUDA(cudaMemcpyAsync(s.host_control, s.control, sizeof(Control), cudaMemcpyDeviceToHost, s.stream));
   synchronize(s);
   s.context = size_t(s.host_control->context);
+  s.bound = s.context;
 }
+
+// A step that would pass the capacity refuses itself on the device (status bit 0): it and every step chained
+// behind it wrote nothing, so the history stays valid. Thrown outside the drain-and-forget path.
+struct CapacityRefusal : LengthError {
+  using LengthError::LengthError;
+};
 
 void check_status(ei_session& s) {
   if (s.host_control->status) {
     const int status = s.host_control->status;
-    // Clear the flag on the device; the step that raised it wrote nothing.
+    // Clear the flag on the device.
     const int zero = 0;
     EI_CUDA(cudaMemcpyAsync(&s.control->status, &zero, sizeof(int), cudaMemcpyHostToDevice, s.stream));
     synchronize(s);
     if (status & 2) throw std::invalid_argument("Session token id exceeds vocabulary");
     if (status & 4) throw std::runtime_error("A bounded wait inside a kernel gave up");
-    throw LengthError("Session context capacity exhausted");
+    throw CapacityRefusal("Session context capacity exhausted");
   }
 }
 
@@ -860,8 +858,7 @@ ei_status ei_session_create(ei_model* model, size_t capacity, int graph, ei_sess
     s->use_graph = graph != 0;
     const size_t H = c.hidden_size, V = c.vocab_size, F = c.intermediate_size;
     const size_t qkv_width = (c.n_heads + 2 * c.n_kv_heads) * 128, kv_width = c.n_kv_heads * 128;
-    s->attention_chunk = attention_chunk_for(capacity);
-    s->attention_splits = int((capacity + s->attention_chunk - 1) / s->attention_chunk);
+    s->attention_splits = attention_grid_splits(capacity, int(c.n_kv_heads), model->multiprocessors);
     size_t offset = 0;
     auto take = [&](size_t bytes) {
       const size_t at = offset;
@@ -957,6 +954,7 @@ ei_status ei_session_prefill(ei_session* session, const uint32_t* host_tokens, s
       // A prefill replaces the history (the reference resizes the managed cache to `rows`).
       EI_CUDA(cudaMemsetAsync(s.control, 0, sizeof(Control), s.stream));
       s.context = 0;
+      s.bound = 0;
       s.history_ready = false;
       for (size_t first = 0; first < rows; first += kMaxRows) {
         const int chunk = int(std::min<size_t>(kMaxRows, rows - first));
@@ -980,6 +978,8 @@ ei_status ei_session_prefill(ei_session* session, const uint32_t* host_tokens, s
       }
       read_control(s);
       check_status(s);
+    } catch (const CapacityRefusal&) {
+      throw;  // refused on the device before any write: the history stays
     } catch (...) {
       drain_failed(s);
       throw;
@@ -1004,6 +1004,8 @@ ei_status ei_session_decode(ei_session* session, uint32_t token, const void** lo
       submit_step(s, 1, kCommitAllWithHead);
       read_control(s);
       check_status(s);
+    } catch (const CapacityRefusal&) {
+      throw;  // refused on the device before any write: the history stays
     } catch (...) {
       drain_failed(s);
       throw;
@@ -1032,6 +1034,8 @@ ei_status ei_session_verify(ei_session* session, const uint32_t* host_tokens, si
       submit_step(s, int(rows), kVerifyHost);
       read_control(s);
       check_status(s);
+    } catch (const CapacityRefusal&) {
+      throw;  // refused on the device before any write: the history stays
     } catch (...) {
       drain_failed(s);
       throw;
@@ -1118,6 +1122,9 @@ ei_status ei_session_verify_enqueue(ei_session* session, const uint32_t* device_
     if (!rows || rows > kMaxRows || (rows > 1 && !device_drafts))
       throw std::invalid_argument("Verify takes 1..16 rows and a device draft array");
     if (!s.history_ready) throw std::logic_error("Verify requires successful prefill");
+    // The host does not know the context length between drains: it bounds it by full acceptance and refuses,
+    // before anything is submitted, a step that could pass the capacity.
+    if (s.bound + rows > s.capacity) throw LengthError("Verify rows could exceed session capacity; drain first");
     require_device(s);
     try {
       if (s.draft_host.drafts != device_drafts || s.draft_host.base != (long long)draft_base ||
@@ -1128,6 +1135,8 @@ ei_status ei_session_verify_enqueue(ei_session* session, const uint32_t* device_
         synchronize(s);
       }
       submit_step(s, int(rows), kVerifyDevice);
+    } catch (const CapacityRefusal&) {
+      throw;  // refused on the device before any write: the history stays
     } catch (...) {
       drain_failed(s);
       throw;
@@ -1152,6 +1161,8 @@ ei_status ei_session_drain(ei_session* session, ei_verify_result* last, uint64_t
       EI_CUDA(cudaMemcpyAsync(&s.control->emitted_total, &zero_total, sizeof(zero_total), cudaMemcpyHostToDevice, s.stream));
       synchronize(s);
       check_status(s);
+    } catch (const CapacityRefusal&) {
+      throw;  // refused on the device before any write: the history stays
     } catch (...) {
       drain_failed(s);
       throw;
@@ -1169,6 +1180,7 @@ ei_status ei_session_truncate(ei_session* session, size_t length) {
     EI_CUDA(cudaMemcpyAsync(&s.control->context, &value, sizeof(value), cudaMemcpyHostToDevice, s.stream));
     synchronize(s);
     s.context = length;
+    s.bound = length;
   });
 }
 
@@ -1192,6 +1204,7 @@ ei_status ei_session_reset(ei_session* session) {
     EI_CUDA(cudaMemsetAsync(s.control, 0, sizeof(Control), s.stream));
     synchronize(s);
     s.context = 0;
+    s.bound = 0;
     s.history_ready = false;
   });
 }
@@ -1443,6 +1456,13 @@ ei_status ei_speculative_truncate(ei_speculative* spec, size_t generated) {
       s->context = size_t(context);
     }
     spec->bound = size_t(context);
+  });
+}
+
+ei_status ei_session_inject_wait_timeout(ei_session* session, uint32_t polls) {
+  return guarded([&] {
+    if (!session || !polls) throw std::invalid_argument("session is null or the poll limit is zero");
+    session->inject_wait_polls = polls;
   });
 }
 

@@ -133,7 +133,6 @@ __global__ void __launch_bounds__(512) finalize_kernel(const float* best_value, 
                                                        Control* control, int32_t* context_length,
                                                        uint32_t* pending, ei_verify_result* result,
                                                        const TokenSink* sink) {
-  EI_TIMELINE_SCOPE(kTimelineFinalize);
   __shared__ uint32_t chosen[16];
   grid_dependency_wait();
   const int row = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -198,5 +197,3 @@ void launch_adopt_control(Control* mine, const Control* theirs, cudaStream_t str
 }
 
 }  // namespace ei
-
-EI_TIMELINE_EXPORT(sampling)

@@ -202,6 +202,8 @@ void launch_awq(const GemmPlan& plan, const GemmParams& p, cudaStream_t stream, 
   cfg.zero_box = cfg.tma_sz ? std::min(4, p.zero_stride) : 0;
   if (!cfg.tma_sz) cfg.sz_boxes = cfg.sz_rows = 0;
   cfg.stages = kAwqMaxStages;
+  cfg.wait_limit = p.wait_limit;
+  cfg.extra_tx = p.fault_tx;
   while (cfg.stages > kAwqPhaseTiles && awq_layout(cfg).total > plan.smem_limit) cfg.stages -= kAwqPhaseTiles;
   const size_t smem = awq_layout(cfg).total;
   if (smem > plan.smem_limit) throw std::invalid_argument("small-M int4 GEMM does not fit in shared memory");
@@ -246,6 +248,8 @@ void launch_dense_tma(const GemmPlan& plan, const GemmParams& p, cudaStream_t st
   DenseLaunch cfg{};
   cfg.units_box = std::min(64, ((parts_total + plan.ksplit - 1) / plan.ksplit) * 4);  // the largest slice
   cfg.stages = kDenseMaxStages;
+  cfg.wait_limit = p.wait_limit;
+  cfg.extra_tx = p.fault_tx;
   while (cfg.stages > 2 && dense_layout(cfg).total > plan.smem_limit) --cfg.stages;
   const size_t smem = dense_layout(cfg).total;
   CUtensorMap weights{};
@@ -284,5 +288,3 @@ void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& p, cudaStream
 }
 
 }  // namespace ei
-
-EI_TIMELINE_EXPORT(smallm_gemm)

@@ -54,6 +54,9 @@ struct GemmParams {
   float* best_value;      // kEpiArgmax: [grid, 16]
   int* best_index;        //             [grid, 16]
   int* status;            // optional device word; bit 2 is set if a bounded wait on a bulk copy gave up
+  uint32_t wait_limit;    // polls before a bounded wait gives up (0: the kernel's default)
+  uint32_t fault_tx;      // test hook: bytes the first weight copy is expected to deliver beyond what it does,
+                          // so that the bounded waits run out (0 in production)
 };
 
 constexpr int kGemmWarps = 16;

@@ -199,6 +199,10 @@ class Session:
     def inject_failure(self, nth_launch: int = 0, completion: bool = False) -> None:
         abi.check(self._lib.ei_session_inject_failure(self._handle, nth_launch, 1 if completion else 0))
 
+    def inject_wait_timeout(self, polls: int) -> None:
+        """Test hook: the next weight-streaming GEMM's bounded waits run out after `polls` polls."""
+        abi.check(self._lib.ei_session_inject_wait_timeout(self._handle, polls))
+
     def close(self) -> None:
         if self._handle:
             self._lib.ei_session_destroy(self._handle)

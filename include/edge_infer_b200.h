@@ -321,6 +321,14 @@ ei_status ei_speculative_truncate(ei_speculative* spec, size_t generated);
  * ref: runtime/tests/qwen3_session_test.cpp:26-70 (link-time --wrap of cublasGemmEx / cudaStreamSynchronize). */
 ei_status ei_session_inject_failure(ei_session* session, int nth_launch, int completion);
 
+/* Test hook for the bounded device waits (no GPU fault, trap or endless loop is involved): the next
+ * weight-streaming GEMM of this session runs outside any captured graph with a poll limit of `polls` and is
+ * told to expect 16 bytes more than its first weight copy delivers, so the copy's barrier never completes, the
+ * waits run out, the kernel returns and raises status bit 2. The step then reports EI_RUNTIME, the session's
+ * own stream is drained and its history forgotten (prefill again); other sessions are untouched.
+ * ref: the drain-or-poison rules of runtime/src/qwen3.cpp:127-161. No counterpart in the reference's API. */
+ei_status ei_session_inject_wait_timeout(ei_session* session, uint32_t polls);
+
 #ifdef __cplusplus
 }
 #endif

@@ -103,6 +103,17 @@ def reference_library() -> C.CDLL:
         lib.ref_cuda_size.argtypes = [C.c_void_p]
         lib.ref_cuda_resize.argtypes = [C.c_void_p, C.c_uint64]
         lib.ref_cuda_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        # direct operators on device pointers (absent from a library built before they were added)
+        if hasattr(lib, "ref_op_rms_norm"):
+            P, U = C.c_void_p, C.c_uint64
+            lib.ref_op_rms_norm.argtypes = [P, P, P, U, U, C.c_float]
+            lib.ref_op_add.argtypes = [P, P, P, U]
+            lib.ref_op_silu_multiply.argtypes = [P, P, P, U]
+            lib.ref_op_rope_precomputed.argtypes = [P, U, U, U, P, U, U]
+            lib.ref_op_store_kv.argtypes = [P, P, U, U, U, U]
+            lib.ref_op_awq_linear.argtypes = [P, U, U, U, P, P, U, P, U, P, P]
+            lib.ref_op_linear.argtypes = [P, U, U, U, P, P, P]
+            lib.ref_op_attention_prefill.argtypes = [P, P, P, P, U, U, U, U, U, U]
         _ref = lib
     return _ref
 
@@ -384,3 +395,50 @@ class ReferenceCuda:
             self.lib.ref_cuda_destroy(self.handle)
         except Exception:
             pass
+
+
+class ReferenceOps:
+    """The unmodified reference's direct CUDA operators (op::cuda::*, BF16) on DEVICE pointers of the current GPU.
+    Arguments are objects with a data_ptr() (torch CUDA tensors); every call returns after a stream synchronise."""
+
+    def __init__(self):
+        self.lib = reference_library()
+        if not hasattr(self.lib, "ref_op_rms_norm"):
+            raise RuntimeError("oracle/_ref was built without the operator entry points; run `make -C oracle ref`")
+
+    def _check(self, status: int) -> None:
+        if status:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+
+    @staticmethod
+    def _p(tensor):
+        return C.c_void_p(tensor.data_ptr()) if tensor is not None else None
+
+    def rms_norm(self, x, weight, out, rows: int, features: int, eps: float) -> None:
+        self._check(self.lib.ref_op_rms_norm(self._p(x), self._p(weight), self._p(out), rows, features, eps))
+
+    def add(self, a, b, out, count: int) -> None:
+        self._check(self.lib.ref_op_add(self._p(a), self._p(b), self._p(out), count))
+
+    def silu_multiply(self, gate, up, out, count: int) -> None:
+        self._check(self.lib.ref_op_silu_multiply(self._p(gate), self._p(up), self._p(out), count))
+
+    def rope_precomputed(self, data, rows: int, heads: int, head_dim: int, table, positions: int, offset: int) -> None:
+        self._check(self.lib.ref_op_rope_precomputed(self._p(data), rows, heads, head_dim, self._p(table), positions,
+                                                     offset))
+
+    def store_kv(self, source, cache, rows: int, width: int, capacity: int, offset: int) -> None:
+        self._check(self.lib.ref_op_store_kv(self._p(source), self._p(cache), rows, width, capacity, offset))
+
+    def awq_linear(self, x, rows: int, k: int, n: int, qweight, scales, padded_groups: int, zeros, group: int, bias,
+                   out) -> None:
+        self._check(self.lib.ref_op_awq_linear(self._p(x), rows, k, n, self._p(qweight), self._p(scales), padded_groups,
+                                               self._p(zeros), group, self._p(bias), self._p(out)))
+
+    def linear(self, x, rows: int, k: int, n: int, weight, bias, out) -> None:
+        self._check(self.lib.ref_op_linear(self._p(x), rows, k, n, self._p(weight), self._p(bias), self._p(out)))
+
+    def attention_prefill(self, q, k, v, out, rows: int, heads: int, kv_heads: int, head_dim: int, length: int,
+                          offset: int) -> None:
+        self._check(self.lib.ref_op_attention_prefill(self._p(q), self._p(k), self._p(v), self._p(out), rows, heads,
+                                                      kv_heads, head_dim, length, offset))

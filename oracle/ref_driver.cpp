@@ -10,6 +10,8 @@
 //   KVCache<T>                           runtime/include/inference.hpp:31-138
 //   Qwen3Model<bf16> / Qwen3Session<bf16> runtime/include/models/qwen3_model.hpp, runtime/src/qwen3.cpp
 //   op::cuda::sample                     operators/src/cuda/execution.cu:463-498
+//   op::cuda::{rms_norm, add, silu_multiply, rope_precomputed, store_kv, awq_linear, linear,
+//              attention_prefill}       operators/include/operators/cuda/execution.hpp:55-124
 #include <cstdint>
 #include <cstring>
 #include <memory>
@@ -235,6 +237,121 @@ int ref_cuda_forward(void* h, const uint32_t* tokens, int rows, uint16_t* logits
     if (logits)
       CUDA_CHECK(cudaMemcpy(logits, out.data, size_t(rows) * vocab * sizeof(T), cudaMemcpyDeviceToHost));
     CUDA_CHECK(cudaMemcpy(greedy, handle->sampled.data_ptr(), rows * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  });
+}
+
+// ---------------------------------------------------------------- CUDA operators
+// The reference's own direct operators on caller-owned DEVICE buffers (BF16 unless noted), on the
+// default stream, followed by a stream synchronisation. Used to compare single operators on
+// identical device inputs on the same GPU.
+namespace {
+using B = __nv_bfloat16;
+op::cuda::ExecutionContext& operator_context() {
+  static cublasHandle_t handle = [] {
+    cublasHandle_t h = nullptr;
+    if (cublasCreate(&h) != CUBLAS_STATUS_SUCCESS) throw std::runtime_error("cublasCreate failed");
+    return h;
+  }();
+  static op::cuda::ExecutionContext context = op::cuda::prepare_execution_context(handle, nullptr);
+  op::cuda::bind_execution_context(context);
+  return context;
+}
+void finish_operator() { CUDA_CHECK(cudaStreamSynchronize(nullptr)); }
+}  // namespace
+
+int ref_op_rms_norm(const void* in, const void* weight, void* out, uint64_t rows, uint64_t features, float eps) {
+  return guarded([&] {
+    op::cuda::rms_norm<B>(operator_context(), {static_cast<const B*>(in), size_t(rows * features)},
+                          {static_cast<const B*>(weight), size_t(features)},
+                          {static_cast<B*>(out), size_t(rows * features)}, rows, features, eps);
+    finish_operator();
+  });
+}
+
+int ref_op_add(const void* a, const void* b, void* out, uint64_t count) {
+  return guarded([&] {
+    op::cuda::add<B>(operator_context(), {static_cast<const B*>(a), size_t(count)},
+                     {static_cast<const B*>(b), size_t(count)}, {static_cast<B*>(out), size_t(count)});
+    finish_operator();
+  });
+}
+
+int ref_op_silu_multiply(const void* gate, const void* up, void* out, uint64_t count) {
+  return guarded([&] {
+    op::cuda::silu_multiply<B>({static_cast<const B*>(gate), size_t(count)}, {static_cast<const B*>(up), size_t(count)},
+                               {static_cast<B*>(out), size_t(count)}, nullptr);
+    finish_operator();
+  });
+}
+
+// data: [rows, heads, head_dim] contiguous, rotated in place; table: float [positions, head_dim].
+int ref_op_rope_precomputed(void* data, uint64_t rows, uint64_t heads, uint64_t head_dim, const float* table,
+                            uint64_t positions, uint64_t offset) {
+  return guarded([&] {
+    TensorView<B, 3> view{static_cast<B*>(data), {size_t(rows), size_t(heads), size_t(head_dim)},
+                          {size_t(heads * head_dim), size_t(head_dim), 1}};
+    TensorView<const float, 2> cache{table, {size_t(positions), size_t(head_dim)}, {size_t(head_dim), 1}};
+    op::cuda::rope_precomputed<B>(operator_context(), view, cache, offset);
+    finish_operator();
+  });
+}
+
+// source: [rows, width]; cache: [capacity, width]; rows are written at `offset`.
+int ref_op_store_kv(const void* source, void* cache, uint64_t rows, uint64_t width, uint64_t capacity, uint64_t offset) {
+  return guarded([&] {
+    TensorView<const B, 2> src{static_cast<const B*>(source), {size_t(rows), size_t(width)}, {size_t(width), 1}};
+    TensorView<B, 2> dst{static_cast<B*>(cache), {size_t(capacity), size_t(width)}, {size_t(width), 1}};
+    op::cuda::store_kv<B>(operator_context(), src, dst, offset);
+    finish_operator();
+  });
+}
+
+// qweight int32 [N, K/8], scales BF16 [N, padded_groups], zeros int32 [N, ceil(K/group/8)], bias BF16 [N] or null.
+int ref_op_awq_linear(const void* x, uint64_t rows, uint64_t K, uint64_t N, const int32_t* qweight, const void* scales,
+                      uint64_t padded_groups, const int32_t* zeros, uint64_t group_size, const void* bias, void* out) {
+  return guarded([&] {
+    const size_t groups = (K + group_size - 1) / group_size;
+    TensorView<const int32_t, 2> q{qweight, {size_t(N), size_t((K + 7) / 8)}, {size_t((K + 7) / 8), 1}};
+    TensorView<const B, 2> s{static_cast<const B*>(scales), {size_t(N), size_t(padded_groups)}, {size_t(padded_groups), 1}};
+    TensorView<const int32_t, 2> z{zeros, {size_t(N), (groups + 7) / 8}, {(groups + 7) / 8, 1}};
+    TensorView<const B, 1> b{};
+    if (bias) b = TensorView<const B, 1>{static_cast<const B*>(bias), {size_t(N)}, {1}};
+    const auto weight = op::cuda::prepare_awq<B>(q, s, z, group_size, K, b);
+    TensorView<const B, 2> input{static_cast<const B*>(x), {size_t(rows), size_t(K)}, {size_t(K), 1}};
+    TensorView<B, 2> output{static_cast<B*>(out), {size_t(rows), size_t(N)}, {size_t(N), 1}};
+    op::cuda::awq_linear<B>(operator_context(), input, weight, output);
+    finish_operator();
+  });
+}
+
+// weight: BF16 physically [N, K] row-major (the checkpoint layout), presented as the logical [K, N] view.
+int ref_op_linear(const void* x, uint64_t rows, uint64_t K, uint64_t N, const void* weight, const void* bias, void* out) {
+  return guarded([&] {
+    TensorView<const B, 2> w{static_cast<const B*>(weight), {size_t(K), size_t(N)}, {1, size_t(K)}};
+    TensorView<const B, 1> b{};
+    if (bias) b = TensorView<const B, 1>{static_cast<const B*>(bias), {size_t(N)}, {1}};
+    const auto prepared = op::cuda::prepare_dense<B>(w, b);
+    TensorView<const B, 2> input{static_cast<const B*>(x), {size_t(rows), size_t(K)}, {size_t(K), 1}};
+    TensorView<B, 2> output{static_cast<B*>(out), {size_t(rows), size_t(N)}, {size_t(N), 1}};
+    op::cuda::linear<B>(operator_context(), input, prepared, output);
+    finish_operator();
+  });
+}
+
+// q, out: [rows, heads, 128]; k, v: [length, kv_heads, 128] with length = offset + rows.
+int ref_op_attention_prefill(const void* q, const void* k, const void* v, void* out, uint64_t rows, uint64_t heads,
+                             uint64_t kv_heads, uint64_t head_dim, uint64_t length, uint64_t offset) {
+  return guarded([&] {
+    TensorView<const B, 3> qv{static_cast<const B*>(q), {size_t(rows), size_t(heads), size_t(head_dim)},
+                              {size_t(heads * head_dim), size_t(head_dim), 1}};
+    TensorView<const B, 3> kv{static_cast<const B*>(k), {size_t(length), size_t(kv_heads), size_t(head_dim)},
+                              {size_t(kv_heads * head_dim), size_t(head_dim), 1}};
+    TensorView<const B, 3> vv{static_cast<const B*>(v), {size_t(length), size_t(kv_heads), size_t(head_dim)},
+                              {size_t(kv_heads * head_dim), size_t(head_dim), 1}};
+    TensorView<B, 3> ov{static_cast<B*>(out), {size_t(rows), size_t(heads), size_t(head_dim)},
+                        {size_t(heads * head_dim), size_t(head_dim), 1}};
+    op::cuda::attention_prefill<B>(operator_context(), qv, kv, vv, ov, offset);
+    finish_operator();
   });
 }
 

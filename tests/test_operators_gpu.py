@@ -5,7 +5,11 @@ attention    |a - e| <= 2.5e-4 + 0.008 max(|a|,|e|) against the reference CPU ex
              bound the reference gives its FP32-numerator decode kernels
              (operators/tests/operators_cuda_attention_precision_test.cu:108), because the verify kernel, like the
              reference's prefill kernel, rounds the softmax numerators to BF16
-norm / rope / silu*up / add: bit-exact BF16 (operators/tests/operators_cuda_bf16_contract_test.cu)."""
+rope / add / gather / store_kv / greedy / accept: bit-exact BF16 against the oracle's host formulas.
+norm / silu*up: compared here with HOST formulas, whose 1/sqrt and exp differ from the device's rsqrt / ex2 in the
+             last FP32 bit, so a BF16 rounding flips in well under 1 % of the outputs (rate asserted below); bit
+             equality of these two is pinned against the reference's own CUDA kernels on the same GPU in
+             tests/test_reference_ops_gpu.py (operators/tests/operators_cuda_bf16_contract_test.cu:66-139, 235-268)."""
 import numpy as np
 import pytest
 
@@ -230,7 +234,7 @@ def test_dense_bias_before_rounding_known_answer(cuda, package, ctx):
 
 
 @pytest.mark.parametrize("width", [7, 128, 1024, 4096, 10240])
-def test_rms_norm_bit_exact(cuda, package, oracle, ctx, width):
+def test_rms_norm_against_host_formula(cuda, package, oracle, ctx, width):
     torch, ops, syn = cuda, package.operators, package.synthetic
     rows = 5
     rng = np.random.default_rng(width)
@@ -254,7 +258,7 @@ def test_rms_norm_bit_exact(cuda, package, oracle, ctx, width):
                      torch.empty(10241, dtype=torch.bfloat16, device="cuda"), 1, 10241, 1e-6)
 
 
-def test_rms_norm_reference_fixture_exact(cuda, package, ctx):
+def test_rms_norm_reference_fixture_against_host_formula(cuda, package, ctx):
     """The reference's own fixture (operators_cuda_bf16_contract_test.cu:235-268) with its scalar expectation."""
     torch, ops, syn = cuda, package.operators, package.synthetic
     width = 128
@@ -313,7 +317,7 @@ def test_rope_small_angle_basis(cuda, package, ctx):
 
 
 @pytest.mark.parametrize("count", [17, 18, 4098, 4099])
-def test_add_and_silu_multiply_bit_exact(cuda, package, oracle, ctx, count):
+def test_add_exact_and_silu_multiply_against_host_formula(cuda, package, oracle, ctx, count):
     torch, ops, syn = cuda, package.operators, package.synthetic
     rng = np.random.default_rng(count)
     a = syn.float_to_bf16(rng.standard_normal(count, dtype=np.float32) * 4)

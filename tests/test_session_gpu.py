@@ -356,3 +356,63 @@ def test_device_resident_loop_equals_host_driven_loop(cuda, package):
     last, total = device.drain()
     assert total == sum(accepts)
     assert last.context == host.context_size() == device.context_size()
+
+
+def test_bounded_device_wait_runs_out_and_is_reported(cuda, package):
+    """A bounded wait inside a kernel that runs out (no fault, trap or endless loop: the first weight copy's
+    barrier is told to expect 16 bytes more than the copy delivers, with a short poll limit) makes the kernel
+    return and raise its status bit. The step reports a runtime error, the session's stream is drained and its
+    history forgotten - the drain rule of the reference (runtime/src/qwen3.cpp:127-161) - the same session
+    recovers with a prefill, and a sibling session of the same model is untouched."""
+    syn, abi = package.synthetic, package.abi
+    for name in ("qwen3_awq", "qwen3_bf16_tied"):                 # the int4 kernel and the dense BF16 kernel
+        shape = shapes(package)[name]
+        model = package.Model(shape, syn.make_model(shape, seed=1))
+        session, sibling = model.new_session(64, graph=True), model.new_session(64, graph=True)
+        sibling.prefill([4, 5, 6])
+        sibling_logits = sibling.read_logits(1).copy()
+        session.prefill([1, 2, 3])
+        reference_logits = session.read_logits(1).copy()
+        first = session.verify([7, 8, 9])
+        session.truncate(3)
+        session.inject_wait_timeout(2000)
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            session.verify([7, 8, 9])
+        assert session.context_size() == 0                        # history forgotten, storage kept
+        with pytest.raises(abi.LogicError):
+            session.verify([7, 8, 9])
+        session.prefill([1, 2, 3])                                # the same session recovers ...
+        assert np.array_equal(session.read_logits(1), reference_logits)
+        again = session.verify([7, 8, 9])                         # ... and the hook was one launch only
+        assert again.targets == first.targets and again.emitted == first.emitted
+        out = sibling.verify([7, 8])
+        assert out.emitted >= 1
+        sibling.prefill([4, 5, 6])
+        assert np.array_equal(sibling.read_logits(1), sibling_logits)
+
+
+def test_enqueue_refuses_steps_that_could_pass_the_capacity(cuda, package):
+    """Between drains the host bounds the context length by full acceptance: a chained step that could pass the
+    capacity is refused before anything is submitted, the history stays, and the chain continues after a drain."""
+    torch, syn, abi = cuda, package.synthetic, package.abi
+    shape = shapes(package)["qwen3_awq"]
+    model = package.Model(shape, syn.make_model(shape, seed=3))
+    session = model.new_session(32, graph=True)
+    session.prefill([1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+    session.set_pending(11)
+    drafts = torch.zeros(64, dtype=torch.int32, device="cuda")
+    session.verify_enqueue(drafts, 0, 9)                          # bound 10 -> 19
+    session.verify_enqueue(drafts, 0, 9)                          # bound 19 -> 28
+    with pytest.raises(abi.LengthError):
+        session.verify_enqueue(drafts, 0, 9)                      # 28 + 9 > 32: refused, nothing submitted
+    last, total = session.drain()
+    context = session.context_size()
+    assert 12 <= context <= 28 and last.context == context and total == context - 10
+    kv = session.read_kv(0)
+    with pytest.raises(abi.LengthError):
+        session.verify_enqueue(drafts, 0, 32 - context + 1)
+    assert session.context_size() == context and np.array_equal(session.read_kv(0)[0], kv[0])
+    if context + 2 <= 32:
+        session.verify_enqueue(drafts, 0, 2)                      # the history is intact: the chain goes on
+        last, _ = session.drain()
+        assert last.context == session.context_size() > context

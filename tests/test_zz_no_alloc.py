@@ -31,13 +31,16 @@ def test_static_scratch_attention_matches_caller_scratch():
         expected = torch.empty_like(dq)
         scratch = torch.empty(ops.attention_scratch_bytes(rows, heads, d, length), dtype=torch.uint8, device="cuda")
         ops.attention_prefill(ctx, dq, dk, dv, expected, length - rows, scratch)
-        torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
         got = torch.full_like(dq, 7.0)
-        baseline = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        # Free device memory as the DRIVER sees it (cudaMemGetInfo): an allocation made inside the library would
+        # not show in torch's own allocator statistics. The first call may load the kernel's module, so the
+        # comparison brackets the second call.
+        free_before = torch.cuda.mem_get_info()[0] if call else None
         ops.attention_prefill_static(ctx, dq, dk, dv, got, length - rows)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == baseline and baseline >= before
+        if call:
+            assert torch.cuda.mem_get_info()[0] >= free_before
         assert torch.equal(got.view(torch.int16), expected.view(torch.int16)), call
 
 
