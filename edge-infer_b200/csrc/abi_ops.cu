@@ -421,7 +421,8 @@ static void run_attention(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view
   p.capacity = int(k.shape[0]);
   p.device_offset = device_offset;
   p.host_offset = int(offset);
-  p.max_splits = attention_grid_splits(length, p.kv_heads, ctx->multiprocessors);
+  p.chunk = attention_chunk_for(length);
+  p.max_splits = int((length + p.chunk - 1) / p.chunk);
   p.scratch = static_cast<float*>(scratch);
   p.out = static_cast<bf16*>(out.data);
   p.out_stride = int(out.stride[0]);

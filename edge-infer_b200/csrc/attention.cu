@@ -11,15 +11,7 @@
 // (operators/src/cuda/kernels/flash_attn_prefill.cu:236-252). Chunks write (o, m, l) partials to
 // caller scratch and a second kernel merges the live chunks in FP32 and rounds once.
 // The position of the first query row is read from device memory, so a captured graph can be
-// replayed while the context grows: a fixed grid of splits per KV head is launched (about one block per
-// multiprocessor over all KV heads) and every block derives its share of whole tiles from the live length.
-//
-// Inside a session's step the kernel also does what precedes attention in the reference's decoder
-// (runtime/include/execution/decoder.hpp:122-147): per-head RMSNorm of q and k, RoPE from the FP32 table, and
-// the append of the step's K/V rows to the cache. Every block normalises and rotates the query rows of its
-// KV group itself, straight into its MMA fragments (a few thousand values: cheaper than a kernel launch);
-// the block whose tiles hold the step's positions normalises, rotates and stores the new K rows and copies the
-// new V rows before it fetches those tiles.
+// replayed while the context grows; blocks beyond the live length return immediately.
 #include "kernels.cuh"
 
 #include <cfloat>
@@ -68,107 +60,22 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                : "r"(address));
 }
 
-// Tiles a block owns for a live length: the fixed grid of p.max_splits blocks per KV head shares the whole tiles.
-__device__ __forceinline__ int tiles_per_split(int length, int max_splits) {
-  const int tiles = (length + kTile - 1) / kTile;
-  return max(1, (tiles + max_splits - 1) / max_splits);
-}
-
-__device__ __forceinline__ void rotate_rounded(float x, float y, float sine, float cosine, float& first, float& second) {
-  sine = round_bf16(sine);
-  cosine = round_bf16(cosine);
-  first = round_bf16(round_bf16(x * cosine) - round_bf16(y * sine));
-  second = round_bf16(round_bf16(x * sine) + round_bf16(y * cosine));
-}
-
-// Sum of squares of a 128-wide head row in the order of the reference's norm kernel
-// (operators/src/cuda/rms_norm_cuda.cu:27-72 run over [rows * heads, 128]: one element per thread, a shuffle tree
-// over each block of 32 elements - offsets 16, 8, 4, 2, 1 - and the four block sums combined as
-// (p0 + p2) + (p1 + p3)), so that the inverse RMS has the reference's bits.
-// Warp form: lane l holds elements 2l, 2l+1 (x0, x1) and 64+2l, 64+2l+1 (y0, y1).
-__device__ __forceinline__ float head_inverse_rms_by_warp(float x0, float x1, float y0, float y1, float eps) {
-  float a = x0 * x0, b = x1 * x1, a2 = y0 * y0, b2 = y1 * y1;
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) {  // element offsets 16, 8, 4, 2 inside a block of 32 elements = 16 lanes
-    a += __shfl_xor_sync(0xffffffffu, a, o);
-    b += __shfl_xor_sync(0xffffffffu, b, o);
-    a2 += __shfl_xor_sync(0xffffffffu, a2, o);
-    b2 += __shfl_xor_sync(0xffffffffu, b2, o);
-  }
-  const float q = (a + b) + (a2 + b2);  // lanes 0-15: p0 + p2, lanes 16-31: p1 + p3
-  const float total = q + __shfl_xor_sync(0xffffffffu, q, 16);
-  return rsqrtf(__fdividef(total, 128.0f) + eps);
-}
-// Quad form for MMA fragments: lane c of a quad holds elements 16 kk + 2 c + {0, 1} (regs[kk][0]) and
-// 16 kk + 8 + 2 c + {0, 1} (regs[kk][1]) of the row, kk = 0..7, as packed BF16 pairs.
-__device__ __forceinline__ float head_inverse_rms_by_quad(const uint32_t (&regs)[8][2], float eps) {
-  float block[4];
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {  // elements 32 w .. 32 w + 31 sit in kk = 2 w and 2 w + 1
-    float u[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      auto sq = [e](uint32_t pair) {
-        const float v = e ? bf16_hi(pair) : bf16_lo(pair);
-        return v * v;
-      };
-      const float t = sq(regs[2 * w][0]) + sq(regs[2 * w + 1][0]);   // offsets j and j + 16, j = 2 c + e
-      const float t2 = sq(regs[2 * w][1]) + sq(regs[2 * w + 1][1]);  // j = 8 + 2 c + e
-      u[e] = t + t2;                                                 // j and j + 8
-      u[e] += __shfl_xor_sync(0xffffffffu, u[e], 2);                 // j and j + 4
-      u[e] += __shfl_xor_sync(0xffffffffu, u[e], 1);                 // j and j + 2
-    }
-    block[w] = u[0] + u[1];                                          // j and j + 1
-  }
-  return rsqrtf(__fdividef((block[0] + block[2]) + (block[1] + block[3]), 128.0f) + eps);
-}
-
-// The step's K row (normalised, rotated) and V row of this KV head go to cache position offset + row; one warp
-// per row, lane l owns elements {2l, 2l+1, 64+2l, 64+2l+1} (rotation pairs 2l and 2l+1).
-__device__ __forceinline__ void append_row(const AttentionParams& p, int row, int position, int kv_head, int lane) {
-  const bf16* k_src = p.k_new + size_t(row) * p.new_stride + size_t(kv_head) * kDim;
-  const bf16* v_src = p.v_new + size_t(row) * p.new_stride + size_t(kv_head) * kDim;
-  bf16* k_dst = p.k_store + size_t(position) * p.kv_stride + size_t(kv_head) * kDim;
-  bf16* v_dst = p.v_store + size_t(position) * p.kv_stride + size_t(kv_head) * kDim;
-  *reinterpret_cast<uint2*>(v_dst + lane * 4) = *reinterpret_cast<const uint2*>(v_src + lane * 4);
-  const uint32_t lo = *reinterpret_cast<const uint32_t*>(k_src + 2 * lane);
-  const uint32_t hi = *reinterpret_cast<const uint32_t*>(k_src + 64 + 2 * lane);
-  float x0 = bf16_lo(lo), x1 = bf16_hi(lo), y0 = bf16_lo(hi), y1 = bf16_hi(hi);
-  if (p.k_norm) {
-    const uint32_t wl = *reinterpret_cast<const uint32_t*>(p.k_norm + 2 * lane);
-    const uint32_t wh = *reinterpret_cast<const uint32_t*>(p.k_norm + 64 + 2 * lane);
-    const float inv = head_inverse_rms_by_warp(x0, x1, y0, y1, p.eps);
-    x0 = round_bf16(round_bf16(x0 * inv) * bf16_lo(wl));
-    x1 = round_bf16(round_bf16(x1 * inv) * bf16_hi(wl));
-    y0 = round_bf16(round_bf16(y0 * inv) * bf16_lo(wh));
-    y1 = round_bf16(round_bf16(y1 * inv) * bf16_hi(wh));
-  }
-  const float4 trig = *reinterpret_cast<const float4*>(p.rope_table + size_t(position) * kDim + 4 * lane);
-  float a0, b0, a1, b1;
-  rotate_rounded(x0, y0, trig.x, trig.y, a0, b0);
-  rotate_rounded(x1, y1, trig.z, trig.w, a1, b1);
-  *reinterpret_cast<uint32_t*>(k_dst + 2 * lane) = pack_bf16(a0, a1);
-  *reinterpret_cast<uint32_t*>(k_dst + 64 + 2 * lane) = pack_bf16(b0, b1);
-}
-
-template <bool kFused>
 __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  // The context length was written by the previous step; the preceding kernel of this step only produces the
+  // The context length was written by the previous step; the preceding kernel of this step only appends the
   // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
   const int offset = p.device_offset ? *p.device_offset : p.host_offset;
   const int length = offset + p.rows;
   const int split = blockIdx.x, kv_head = blockIdx.y;
-  if (offset < 0 || length > p.capacity || (kFused && length > p.max_positions)) {
+  const int start = split * p.chunk;
+  if (offset < 0 || length > p.capacity) {
     // The whole grid leaves: it still waits for its predecessor first, so that a successor never sees this
     // kernel complete before the kernels ahead of it have.
     grid_dependency_wait();
     return;
   }
-  const int chunk = tiles_per_split(length, p.max_splits) * kTile;
-  const int start = split * chunk;
   if (start >= length) return;  // other blocks of the grid wait
-  const int end = min(start + chunk, length);
+  const int end = min(start + p.chunk, length);
   const int group = p.heads / p.kv_heads;
   const int stacked = p.rows * group;  // query rows served by this block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
@@ -178,20 +85,8 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   const bf16* k_base = p.k + size_t(kv_head) * kDim;
   const bf16* v_base = p.v + size_t(kv_head) * kDim;
 
-  const bool settled = end <= offset;  // no row of this chunk is produced by this step
-  if (!settled) {
-    grid_dependency_wait();
-    if (kFused) {
-      // This block's tiles hold some of the step's positions: append those rows first, then make them visible
-      // to the asynchronous tile copies of this block.
-      for (int row = warp; row < p.rows; row += int(blockDim.x >> 5)) {
-        const int position = offset + row;
-        if (position >= start && position < end) append_row(p, row, position, kv_head, lane);
-      }
-      __threadfence();
-      __syncthreads();
-    }
-  }
+  const bool settled = end <= offset;  // no row of this chunk is written by the preceding kernel
+  if (!settled) grid_dependency_wait();
   load_tile(k_smem[0], v_smem[0], k_base, v_base, p.kv_stride, start, end);
   cp_async_commit();
   if (settled) grid_dependency_wait();  // the queries come from the preceding kernel
@@ -215,54 +110,6 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
       qa[kk][1] = live_hi ? *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 2 * c) : 0u;
       qa[kk][2] = live_lo ? *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 8 + 2 * c) : 0u;
       qa[kk][3] = live_hi ? *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 8 + 2 * c) : 0u;
-    }
-  }
-  if (kFused) {
-    // Raw projection rows: per-head RMSNorm, then RoPE. The lane holds elements 16 kk + 2 c + {0, 1, 8, 9} of its
-    // two rows, i.e. both elements (d, d + 64) of every rotation pair it touches: pair d sits in qa[kk] and
-    // qa[kk + 4]. The four lanes of a quad hold a whole 128-wide head row between them.
-    if (p.q_norm) {
-      uint32_t row_lo[8][2], row_hi[8][2];
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        row_lo[kk][0] = qa[kk][0];
-        row_lo[kk][1] = qa[kk][2];
-        row_hi[kk][0] = qa[kk][1];
-        row_hi[kk][1] = qa[kk][3];
-      }
-      const float inv_lo = head_inverse_rms_by_quad(row_lo, p.eps), inv_hi = head_inverse_rms_by_quad(row_hi, p.eps);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(p.q_norm + kk * 16 + 2 * c);
-        const uint32_t w2 = *reinterpret_cast<const uint32_t*>(p.q_norm + kk * 16 + 8 + 2 * c);
-        auto normalise = [](uint32_t pair, float inv, uint32_t w) {
-          return pack_bf16(round_bf16(bf16_lo(pair) * inv) * bf16_lo(w), round_bf16(bf16_hi(pair) * inv) * bf16_hi(w));
-        };
-        qa[kk][0] = normalise(qa[kk][0], inv_lo, w0);
-        qa[kk][1] = normalise(qa[kk][1], inv_hi, w0);
-        qa[kk][2] = normalise(qa[kk][2], inv_lo, w2);
-        qa[kk][3] = normalise(qa[kk][3], inv_hi, w2);
-      }
-    }
-    const float* trig_lo = p.rope_table + size_t(offset + r_lo) * kDim;
-    const float* trig_hi = p.rope_table + size_t(offset + r_hi) * kDim;
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {  // elements 16 kk + 8 half + 2 c + {0, 1}: rotation pairs of that index
-        const int pair = kk * 16 + half * 8 + 2 * c;
-#pragma unroll
-        for (int hi = 0; hi < 2; ++hi) {
-          const float4 trig = *reinterpret_cast<const float4*>((hi ? trig_hi : trig_lo) + 2 * pair);
-          uint32_t& x = qa[kk][half * 2 + hi];
-          uint32_t& y = qa[kk + 4][half * 2 + hi];
-          float a0, b0, a1, b1;
-          rotate_rounded(bf16_lo(x), bf16_lo(y), trig.x, trig.y, a0, b0);
-          rotate_rounded(bf16_hi(x), bf16_hi(y), trig.z, trig.w, a1, b1);
-          x = pack_bf16(a0, a1);
-          y = pack_bf16(b0, b1);
-        }
-      }
     }
   }
   // Last visible token of each row (causal): offset + r.
@@ -406,8 +253,7 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   const int slots = p.rows * p.heads;
   const int length = offset + p.rows;
   if (offset < 0 || length > p.capacity) return;  // after the wait above
-  const int chunk = tiles_per_split(length, p.max_splits) * kTile;
-  const int splits = min(64, (length + chunk - 1) / chunk);
+  const int splits = min(64, (length + p.chunk - 1) / p.chunk);
   // This warp's splits (w, w + 4, ...) are requested together with the maxima and sums, so that the block pays
   // one trip to memory instead of two.
   float4 values[16];
@@ -474,14 +320,6 @@ size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length) {
   return splits * rows * heads * kPartial * sizeof(float);
 }
 
-int attention_grid_splits(size_t kv_capacity, int kv_heads, int multiprocessors) {
-  // About one block per multiprocessor over all KV heads, never more than one per tile nor more than the
-  // scratch sized by attention_scratch_bytes holds.
-  const size_t chunk = attention_chunk_for(kv_capacity);
-  const int scratch_splits = int((kv_capacity + chunk - 1) / chunk);
-  return std::max(1, std::min(scratch_splits, std::max(1, multiprocessors / std::max(1, kv_heads))));
-}
-
 void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
   const int group = p.heads / p.kv_heads;
   const int warps = (p.rows * group + 15) / 16;
@@ -489,18 +327,12 @@ void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool
   int device = 0;
   EI_CUDA(cudaGetDevice(&device));
   if (configured_device != device) {
-    EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 4 * kTileBytes));
-    EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  4 * kTileBytes));
     configured_device = device;
   }
-  if (p.k_new)
-    launch(verify_attention_kernel<true>, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
-           stream, pdl, p);
-  else
-    launch(verify_attention_kernel<false>, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
-           stream, pdl, p);
+  launch(verify_attention_kernel, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
+         stream, pdl, p);
   launch(attention_merge_kernel, dim3(p.rows * p.heads), dim3(128), 0, stream, pdl, p);
 }
 

@@ -154,6 +154,86 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
   }
 }
 
+// Inverse RMS of a 128-wide head row with the sum of squares in the order of the reference's norm kernel
+// (operators/src/cuda/rms_norm_cuda.cu:27-72 run over [rows * heads, 128]: one element per thread, a shuffle tree
+// over each block of 32 elements - offsets 16, 8, 4, 2, 1 - and the four block sums combined as
+// (p0 + p2) + (p1 + p3)), so that it has the reference's bits. Lane l of the warp holds elements 2l, 2l+1
+// (x0, x1) and 64+2l, 64+2l+1 (y0, y1).
+__device__ __forceinline__ float head_inverse_rms(float x0, float x1, float y0, float y1, float eps) {
+  float a = x0 * x0, b = x1 * x1, a2 = y0 * y0, b2 = y1 * y1;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {  // element offsets 16, 8, 4, 2 inside a block of 32 elements = 16 lanes
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+    a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+    b2 += __shfl_xor_sync(0xffffffffu, b2, o);
+  }
+  const float q = (a + b) + (a2 + b2);  // lanes 0-15: p0 + p2, lanes 16-31: p1 + p3
+  const float total = q + __shfl_xor_sync(0xffffffffu, q, 16);
+  return rsqrtf(__fdividef(total, 128.0f) + eps);
+}
+
+// One warp per (row, head); lane l owns rotation pairs 2l and 2l+1, i.e. elements
+// {2l, 2l+1} of the first half and {64+2l, 64+2l+1} of the second.
+__global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams p) {
+  const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int per_row = p.heads + 2 * p.kv_heads;
+  if (warp_global >= p.rows * per_row) return;
+  const int row = warp_global / per_row, slot = warp_global - row * per_row;
+  // Read before waiting for the projection: the context length (written by the previous step), the norm
+  // weights and the rotation table do not come from it, so their latency overlaps its tail.
+  const int context = p.control->context;
+  const int position = context + row;
+  if (context + p.rows > p.capacity || position >= p.max_positions) {  // status set by the embed kernel
+    grid_dependency_wait();  // every block leaves here: complete only after the predecessor has
+    return;
+  }
+  const bool is_value = slot >= p.heads + p.kv_heads;
+  const bool is_query = slot < p.heads;
+  const bf16* norm = is_query ? p.q_norm : p.k_norm;
+  uint32_t wl = 0, wh = 0;
+  float4 trig = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (!is_value) {
+    if (norm) {
+      wl = *reinterpret_cast<const uint32_t*>(norm + 2 * lane);
+      wh = *reinterpret_cast<const uint32_t*>(norm + 64 + 2 * lane);
+    }
+    trig = *reinterpret_cast<const float4*>(p.rope_table + size_t(position) * 128 + 4 * lane);
+  }
+  grid_dependency_wait();
+  grid_launch_dependents();
+  bf16* head = p.qkv + size_t(row) * p.qkv_stride + size_t(slot) * 128;
+  if (is_value) {  // value head: append as is
+    const int kvh = slot - p.heads - p.kv_heads;
+    const uint2 v = *reinterpret_cast<const uint2*>(head + lane * 4);
+    *reinterpret_cast<uint2*>(p.v_cache + (size_t(position) * p.kv_heads + kvh) * 128 + lane * 4) = v;
+    return;
+  }
+  const uint32_t lo = *reinterpret_cast<const uint32_t*>(head + 2 * lane);
+  const uint32_t hi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
+  float x0 = bf16_lo(lo), x1 = bf16_hi(lo), y0 = bf16_lo(hi), y1 = bf16_hi(hi);
+  if (norm) {
+    const float inv = head_inverse_rms(x0, x1, y0, y1, p.eps);
+    x0 = round_bf16(round_bf16(x0 * inv) * bf16_lo(wl));
+    x1 = round_bf16(round_bf16(x1 * inv) * bf16_hi(wl));
+    y0 = round_bf16(round_bf16(y0 * inv) * bf16_lo(wh));
+    y1 = round_bf16(round_bf16(y1 * inv) * bf16_hi(wh));
+  }
+  float a0, b0, a1, b1;
+  rotate_pair(x0, y0, trig.x, trig.y, a0, b0);
+  rotate_pair(x1, y1, trig.z, trig.w, a1, b1);
+  const uint32_t out_lo = pack_bf16(a0, a1), out_hi = pack_bf16(b0, b1);
+  if (is_query) {
+    *reinterpret_cast<uint32_t*>(head + 2 * lane) = out_lo;
+    *reinterpret_cast<uint32_t*>(head + 64 + 2 * lane) = out_hi;
+  } else {
+    bf16* dst = p.k_cache + (size_t(position) * p.kv_heads + (slot - p.heads)) * 128;
+    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = out_lo;
+    *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = out_hi;
+  }
+}
+
 // projection = round(sum of the K-slice partials + bias); residual = round(residual + projection);
 // normed = RMSNorm(residual). Thread t owns features t, t + 1024, ... as the reference's norm kernel does, and
 // every load of a thread (residual, bias, norm weights before the dependency wait; the partial slices after it)
@@ -209,6 +289,95 @@ __global__ void __launch_bounds__(kNormThreads) residual_norm_kernel(const Resid
   }
 }
 
+// Vectorised form for hidden % 4 == 0: 1024 threads, each owning up to three groups of four consecutive
+// features. Its sum of squares is taken in this layout's own order, not the reference kernel's: the inverse RMS
+// may differ from the reference's in the last FP32 bit (the element-order form above costs 3 us more per launch,
+// measured, for a difference far below that of the projections' accumulation orders). Every load of a thread (partial slices, bias, residual) is issued before the first use, so a
+// row costs about one memory latency instead of one per slice.
+constexpr int kRowThreads = 1024;
+constexpr int kRowMaxGroups = 3;  // 1024 threads * 4 values * 3 groups >= 10240
+
+__device__ __forceinline__ float4 load4_bf16(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+}
+__device__ __forceinline__ void store4_bf16(bf16* p, float4 v) {
+  uint2 raw;
+  raw.x = pack_bf16(v.x, v.y);
+  raw.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// kRowGroups: groups of 4096 values a row needs (1 for hidden <= 4096), so that small rows keep few registers.
+template <int kRowGroups>
+__global__ void __launch_bounds__(kRowThreads) residual_norm_vec_kernel(const ResidualNormParams p) {
+  __shared__ float shared[32];
+  const int row = blockIdx.x;
+  bf16* residual = p.residual + size_t(row) * p.hidden;
+  bf16* normed = p.normed + size_t(row) * p.hidden;
+  const size_t slice = size_t(p.rows) * p.hidden;
+  const float* partial = p.partial + size_t(row) * p.hidden;
+  const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  // Before waiting for the projection: the residual stream (last written several kernels ago), the bias and
+  // the norm weights do not come from it.
+  float4 old_residual[kRowGroups], bias[kRowGroups], weight[kRowGroups];
+#pragma unroll
+  for (int j = 0; j < kRowGroups; ++j) {
+    const int i = (threadIdx.x + j * kRowThreads) * 4;
+    old_residual[j] = bias[j] = weight[j] = zero;
+    if (i < p.hidden) {
+      old_residual[j] = load4_bf16(residual + i);
+      if (p.bias) bias[j] = load4_bf16(p.bias + i);
+      weight[j] = load4_bf16(p.norm_weight + i);
+    }
+  }
+  grid_dependency_wait();
+  grid_launch_dependents();
+  float4 values[kRowGroups];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kRowGroups; ++j) {
+    const int i = (threadIdx.x + j * kRowThreads) * 4;
+    values[j] = zero;
+    if (i < p.hidden) {
+      const float4 a0 = *reinterpret_cast<const float4*>(partial + i);
+      const float4 a1 = p.ksplit > 1 ? *reinterpret_cast<const float4*>(partial + slice + i) : zero;
+      const float4 a2 = p.ksplit > 2 ? *reinterpret_cast<const float4*>(partial + 2 * slice + i) : zero;
+      const float4 a3 = p.ksplit > 3 ? *reinterpret_cast<const float4*>(partial + 3 * slice + i) : zero;
+      const float4 r = old_residual[j], b = bias[j];
+      float4 projection = make_float4(a0.x + a1.x, a0.y + a1.y, a0.z + a1.z, a0.w + a1.w);
+      projection = make_float4(projection.x + a2.x, projection.y + a2.y, projection.z + a2.z, projection.w + a2.w);
+      projection = make_float4(projection.x + a3.x, projection.y + a3.y, projection.z + a3.z, projection.w + a3.w);
+      for (int s = 4; s < p.ksplit; ++s) {
+        const float4 more = *reinterpret_cast<const float4*>(partial + s * slice + i);
+        projection = make_float4(projection.x + more.x, projection.y + more.y, projection.z + more.z, projection.w + more.w);
+      }
+      float4 v;
+      v.x = round_bf16(r.x + round_bf16(projection.x + b.x));
+      v.y = round_bf16(r.y + round_bf16(projection.y + b.y));
+      v.z = round_bf16(r.z + round_bf16(projection.z + b.z));
+      v.w = round_bf16(r.w + round_bf16(projection.w + b.w));
+      store4_bf16(residual + i, v);
+      values[j] = v;
+      sum = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sum))));
+    }
+  }
+  const float inv = inverse_rms(block_sum(sum, shared), p.hidden, p.eps);
+#pragma unroll
+  for (int j = 0; j < kRowGroups; ++j) {
+    const int i = (threadIdx.x + j * kRowThreads) * 4;
+    if (i < p.hidden) {
+      const float4 w = weight[j];
+      float4 out;
+      out.x = round_bf16(values[j].x * inv) * w.x;
+      out.y = round_bf16(values[j].y * inv) * w.y;
+      out.z = round_bf16(values[j].z * inv) * w.z;
+      out.w = round_bf16(values[j].w * inv) * w.w;
+      store4_bf16(normed + i, out);
+    }
+  }
+}
+
 int blocks_for(size_t count, int multiprocessors) {
   return int(std::max<size_t>(1, std::min<size_t>((count + 255) / 256, size_t(multiprocessors) * 32)));
 }
@@ -257,11 +426,21 @@ void launch_embed_norm(const EmbedParams& p, cudaStream_t stream, bool pdl) {
   launch(embed_norm_kernel, dim3(p.rows), dim3(kNormThreads), 0, stream, pdl, p);
 }
 
+void launch_qk_norm_rope_store(const QkvParams& p, cudaStream_t stream, bool pdl) {
+  const int warps = p.rows * (p.heads + 2 * p.kv_heads);
+  launch(qk_norm_rope_store_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, pdl, p);
+}
+
 void launch_residual_norm(const ResidualNormParams& p, cudaStream_t stream, bool pdl) {
-  if (p.hidden <= kNormThreads * 4)
-    launch(residual_norm_kernel<4>, dim3(p.rows), dim3(kNormThreads), 0, stream, pdl, p);
-  else
+  if (p.hidden % 4 != 0) {
     launch(residual_norm_kernel<kNormMaxPerThread>, dim3(p.rows), dim3(kNormThreads), 0, stream, pdl, p);
+  } else if (p.hidden <= kRowThreads * 4) {
+    launch(residual_norm_vec_kernel<1>, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
+  } else if (p.hidden <= kRowThreads * 8) {
+    launch(residual_norm_vec_kernel<2>, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
+  } else {
+    launch(residual_norm_vec_kernel<kRowMaxGroups>, dim3(p.rows), dim3(kRowThreads), 0, stream, pdl, p);
+  }
 }
 
 }  // namespace ei

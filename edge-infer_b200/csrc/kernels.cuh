@@ -59,6 +59,22 @@ struct EmbedParams {
 // Token selection + embedding lookup + first RMSNorm, one block per row.
 void launch_embed_norm(const EmbedParams& p, cudaStream_t stream, bool pdl);
 
+struct QkvParams {
+  bf16* qkv;                // [rows, (heads + 2 kv_heads) * 128] : q | k | v, q and k rotated in place
+  int rows, heads, kv_heads, qkv_stride;
+  const bf16* q_norm;       // [128] or null
+  const bf16* k_norm;
+  float eps;
+  const float* rope_table;  // [max_pos, 128]
+  int max_positions;
+  const Control* control;
+  int capacity;
+  bf16* k_cache;            // [capacity, kv_heads * 128] of this layer
+  bf16* v_cache;
+};
+// Per-head QK RMSNorm + RoPE + KV append at the device-side context length, one warp per (row, head).
+void launch_qk_norm_rope_store(const QkvParams& p, cudaStream_t stream, bool pdl);
+
 struct ResidualNormParams {
   const float* partial;     // [ksplit, rows, hidden] FP32 partial sums of the projection
   int ksplit, rows, hidden;
@@ -82,27 +98,14 @@ struct AttentionParams {
   int capacity;             // tokens addressable in k / v
   const int32_t* device_offset;  // position of query row 0 (device) or null -> host_offset
   int host_offset;
-  int max_splits;           // blocks launched per KV head (attention_grid_splits); each derives its whole
-                            // tiles from the live length
+  int chunk;                // tokens per split (multiple of 64)
+  int max_splits;
   float* scratch;           // [max_splits][rows * heads][132]
   bf16* out;                // row r, head h at out + r * out_stride + h * 128
   int out_stride;
-  // Fused step prologue (k_new != null): q holds the RAW projection rows; the kernel applies the per-head
-  // RMSNorm (weights may be null) and RoPE to q and to the step's K rows and appends K/V at offset + row.
-  const bf16* k_new;        // row r, kv head j at k_new + r * new_stride + j * 128 (raw projection)
-  const bf16* v_new;
-  int new_stride;
-  bf16* k_store;            // the cache `k` / `v` point into, writable
-  bf16* v_store;
-  const bf16* q_norm;       // [128] or null
-  const bf16* k_norm;
-  float eps;
-  const float* rope_table;  // [max_positions, 128]: (sine, cosine) of rotation pair i at [2 i, 2 i + 1]
-  int max_positions;
 };
 int attention_chunk_for(size_t kv_length);
 size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length);
-int attention_grid_splits(size_t kv_capacity, int kv_heads, int multiprocessors);
 void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);
 
 // ---- sampling.cu ----

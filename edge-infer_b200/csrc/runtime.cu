@@ -271,7 +271,7 @@ struct ei_session {
   uint32_t* host_tokens = nullptr;
   Control* host_control = nullptr;
   // plans
-  int attention_splits = 1;  // blocks per KV head the attention kernel is launched with
+  int attention_chunk = 64, attention_splits = 1;
   // state
   size_t context = 0;
   size_t bound = 0;  // upper bound of the context length after every step enqueued so far (full acceptance)
@@ -476,33 +476,40 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
       run_linear(s, L.qkv, s.normed, rows, kEpiStore, s.qkv, qkv_width, pdl);
     else
       run_generic(s, L.qkv, s.normed, rows, s.qkv, pdl);
-    // q|k|v leave the projection raw: the attention kernel normalises and rotates q and k itself and appends
-    // the step's K/V rows (decoder.hpp:122-147 of the reference, in one launch).
+    QkvParams q{};
+    q.qkv = s.qkv;
+    q.rows = rows;
+    q.heads = heads;
+    q.kv_heads = kv_heads;
+    q.qkv_stride = qkv_width;
+    q.q_norm = c.qk_norm ? L.q_norm : nullptr;
+    q.k_norm = c.qk_norm ? L.k_norm : nullptr;
+    q.eps = c.rms_norm_eps;
+    q.rope_table = m.rope_table;
+    q.max_positions = int(c.max_position_embeddings);
+    q.control = s.control;
+    q.capacity = int(s.capacity);
+    q.k_cache = s.k_cache + layer * s.capacity * kv_width;
+    q.v_cache = s.v_cache + layer * s.capacity * kv_width;
+    tick(s);
+    launch_qk_norm_rope_store(q, s.stream, pdl);
+
     AttentionParams a{};
     a.q = s.qkv;
     a.q_stride = qkv_width;
-    a.k = s.k_cache + layer * s.capacity * kv_width;
-    a.v = s.v_cache + layer * s.capacity * kv_width;
+    a.k = q.k_cache;
+    a.v = q.v_cache;
     a.kv_stride = kv_width;
     a.rows = rows;
     a.heads = heads;
     a.kv_heads = kv_heads;
     a.capacity = int(s.capacity);
     a.device_offset = &s.control->context;
+    a.chunk = s.attention_chunk;
     a.max_splits = s.attention_splits;
     a.scratch = s.attention_scratch;
     a.out = s.attention;
     a.out_stride = heads * 128;
-    a.k_new = s.qkv + heads * 128;
-    a.v_new = s.qkv + (heads + kv_heads) * 128;
-    a.new_stride = qkv_width;
-    a.k_store = s.k_cache + layer * s.capacity * kv_width;
-    a.v_store = s.v_cache + layer * s.capacity * kv_width;
-    a.q_norm = c.qk_norm ? L.q_norm : nullptr;
-    a.k_norm = c.qk_norm ? L.k_norm : nullptr;
-    a.eps = c.rms_norm_eps;
-    a.rope_table = m.rope_table;
-    a.max_positions = int(c.max_position_embeddings);
     tick(s);
     tick(s);
     launch_verify_attention(a, s.stream, pdl);
@@ -623,6 +630,26 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
       run_generic(lead, L.qkv, lead.normed, total, lead.qkv, pdl);
     for (int j = 0; j < count; ++j) {
       ei_session& s = *batch.sessions[j];
+      QkvParams q{};
+      q.qkv = lead.qkv + size_t(j) * rows * qkv_width;
+      q.rows = rows;
+      q.heads = heads;
+      q.kv_heads = kv_heads;
+      q.qkv_stride = qkv_width;
+      q.q_norm = c.qk_norm ? L.q_norm : nullptr;
+      q.k_norm = c.qk_norm ? L.k_norm : nullptr;
+      q.eps = c.rms_norm_eps;
+      q.rope_table = m.rope_table;
+      q.max_positions = int(c.max_position_embeddings);
+      q.control = s.control;
+      q.capacity = int(s.capacity);
+      q.k_cache = s.k_cache + layer * s.capacity * kv_width;
+      q.v_cache = s.v_cache + layer * s.capacity * kv_width;
+      tick(lead);
+      launch_qk_norm_rope_store(q, lead.stream, pdl);
+    }
+    for (int j = 0; j < count; ++j) {
+      ei_session& s = *batch.sessions[j];
       AttentionParams a{};
       a.q = lead.qkv + size_t(j) * rows * qkv_width;
       a.q_stride = qkv_width;
@@ -634,20 +661,11 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
       a.kv_heads = kv_heads;
       a.capacity = int(s.capacity);
       a.device_offset = &s.control->context;
+      a.chunk = s.attention_chunk;
       a.max_splits = s.attention_splits;
       a.scratch = lead.attention_scratch + size_t(j) * scratch_floats;
       a.out = lead.attention + size_t(j) * rows * heads * 128;
       a.out_stride = heads * 128;
-      a.k_new = a.q + heads * 128;
-      a.v_new = a.q + (heads + kv_heads) * 128;
-      a.new_stride = qkv_width;
-      a.k_store = s.k_cache + layer * s.capacity * kv_width;
-      a.v_store = s.v_cache + layer * s.capacity * kv_width;
-      a.q_norm = c.qk_norm ? L.q_norm : nullptr;
-      a.k_norm = c.qk_norm ? L.k_norm : nullptr;
-      a.eps = c.rms_norm_eps;
-      a.rope_table = m.rope_table;
-      a.max_positions = int(c.max_position_embeddings);
       tick(lead);
       tick(lead);
       launch_verify_attention(a, lead.stream, pdl);
@@ -858,7 +876,8 @@ ei_status ei_session_create(ei_model* model, size_t capacity, int graph, ei_sess
     s->use_graph = graph != 0;
     const size_t H = c.hidden_size, V = c.vocab_size, F = c.intermediate_size;
     const size_t qkv_width = (c.n_heads + 2 * c.n_kv_heads) * 128, kv_width = c.n_kv_heads * 128;
-    s->attention_splits = attention_grid_splits(capacity, int(c.n_kv_heads), model->multiprocessors);
+    s->attention_chunk = attention_chunk_for(capacity);
+    s->attention_splits = int((capacity + s->attention_chunk - 1) / s->attention_chunk);
     size_t offset = 0;
     auto take = [&](size_t bytes) {
       const size_t at = offset;
@@ -1135,8 +1154,7 @@ ei_status ei_session_verify_enqueue(ei_session* session, const uint32_t* device_
         synchronize(s);
       }
       submit_step(s, int(rows), kVerifyDevice);
-    } catch (const CapacityRefusal&) {
-      throw;  // refused on the device before any write: the history stays
+      s.bound += rows;
     } catch (...) {
       drain_failed(s);
       throw;

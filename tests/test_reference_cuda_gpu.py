@@ -27,21 +27,25 @@ import pytest
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
-# name -> (rows, p, prompt, steps, capacity, rms bound, element bound, minimum decisive rows).
+# name -> (rows, p, prompt, steps, capacity, rms bound, element bound, minimum decisive rows, minimum share of ALL
+# rows whose greedy token equals the reference's).
 # The element bounds are constants chosen once, about 1.5 x the largest distance measured between this library and
 # the reference CUDA path at that configuration (recorded in the design notes, with the distance between the
 # reference and the exact-accumulation staged oracle where the CPU can follow): 2 - 3 layers 0.013 - 0.030,
 # 8 layers 0.032, 28 layers 0.041 (C3), 36 layers 0.067 (C4). C5 has no QK-norm and random int4 weights: its
 # attention is nearly one-hot and the reference itself moves by 0.27 (rms 0.058) when the same prompt is fed in
 # pieces of five tokens instead of at once, so its bounds are that self-distance, not a kernel property.
+# With random-init weights the logits are flat: at the full shapes next to no row's top-2 gap clears twice the
+# element bound, so there the gate that cannot be vacuous is the share of all rows with the reference's token
+# (measured 0.94 at C3, 0.90 at C4, 0.71 at C5); every decisive row that does occur must still agree.
 BOUNDS = {
-    "qwen3_awq":        (9, 0.3, 83, 5, 256, 1e-2, 3e-2, 5),
-    "qwen3_awq_deep":   (9, 0.3, 83, 5, 256, 1e-2, 5e-2, 5),
-    "qwen3_bf16":       (5, 0.3, 83, 5, 256, 1e-2, 3e-2, 5),
-    "qwen25_awq_bias":  (5, 0.3, 83, 5, 256, 1e-2, 5e-2, 3),
-    "c3_qwen3_1_7b":    (5, 0.3, 512, 16, 1024, 1e-2, 8e-2, 1),
-    "c4_qwen3_8b_awq":  (9, 0.2, 256, 16, 512, 1.5e-2, 1e-1, 1),
-    "c5_qwen25_7b_awq": (5, 0.3, 256, 16, 512, 6e-2, 2.7e-1, 0),
+    "qwen3_awq":        (9, 0.3, 83, 5, 256, 1e-2, 3e-2, 5, 0.9),
+    "qwen3_awq_deep":   (9, 0.3, 83, 5, 256, 1e-2, 5e-2, 5, 0.9),
+    "qwen3_bf16":       (5, 0.3, 83, 5, 256, 1e-2, 3e-2, 5, 0.9),
+    "qwen25_awq_bias":  (5, 0.3, 83, 5, 256, 1e-2, 5e-2, 3, 0.8),
+    "c3_qwen3_1_7b":    (5, 0.3, 512, 16, 1024, 1e-2, 8e-2, 0, 0.85),
+    "c4_qwen3_8b_awq":  (9, 0.2, 256, 16, 512, 1.5e-2, 1e-1, 0, 0.8),
+    "c5_qwen25_7b_awq": (5, 0.3, 256, 16, 512, 6e-2, 2.7e-1, 0, 0.5),
 }
 
 
@@ -79,7 +83,7 @@ def run_against_reference(torch, package, oracle, name, shape, tensors_for_libra
     """`staged`: the CPU oracle at the CUDA path's rounding points with exact accumulation, where the CPU can follow
     the shape; its distance to the reference is recorded beside this library's (not asserted)."""
     syn = package.synthetic
-    rows, p, prompt_len, steps, capacity, rms_bound, element_bound, minimum = BOUNDS[name]
+    rows, p, prompt_len, steps, capacity, rms_bound, element_bound, minimum, equal_share = BOUNDS[name]
     session = package.Model(shape, tensors_for_library).new_session(capacity, graph=True)
     reference = oracle.ReferenceCuda(shape, tensors_for_reference, capacity)
     prompt = syn.make_prompt(12, prompt_len, shape.vocab_size)
@@ -156,6 +160,7 @@ def run_against_reference(torch, package, oracle, name, shape, tensors_for_libra
             handle.write(json.dumps(record) + "\n")
     assert token_mismatches == 0 and accept_mismatches == 0, record
     assert decisive_rows >= minimum, record
+    assert rows_equal >= equal_share * rows_total, record
     del session, reference
     torch.cuda.empty_cache()
 
