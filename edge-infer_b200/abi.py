@@ -149,6 +149,8 @@ PROTOTYPES = {
     "ei_session_read_kv": (_S, [_P, _Z, _P, _P]),
     "ei_session_read_logits": (_S, [_P, _Z, _P]),
     "ei_session_launches_per_step": (_Z, [_P, _Z]),
+    "ei_session_write_kv": (_S, [_P, C.c_size_t, C.c_size_t, C.c_size_t, _P, _P]),
+    "ei_session_adopt_history": (_S, [_P, C.c_size_t, C.c_uint32]),
     "ei_session_inject_failure": (_S, [_P, C.c_int, C.c_int]),
     "ei_session_inject_wait_timeout": (_S, [_P, C.c_uint32]),
 }

@@ -1266,6 +1266,44 @@ ei_status ei_session_read_kv(ei_session* session, size_t layer, void* host_k, vo
   });
 }
 
+ei_status ei_session_write_kv(ei_session* session, size_t layer, size_t first, size_t rows, const void* k,
+                              const void* v) {
+  return guarded([&] {
+    if (!session || !k || !v) throw std::invalid_argument("session or source is null");
+    ei_session& s = *session;
+    require_usable(s);
+    require_device(s);
+    const auto& c = s.model->config;
+    if (layer >= c.n_layers) throw std::out_of_range("KVCache: Layer index out of range");
+    if (first > s.capacity || rows > s.capacity - first) throw LengthError("KV rows exceed session capacity");
+    const size_t kv_width = c.n_kv_heads * 128;
+    const size_t at = (layer * s.capacity + first) * kv_width;
+    EI_CUDA(cudaMemcpyAsync(s.k_cache + at, k, rows * kv_width * 2, cudaMemcpyDefault, s.stream));
+    EI_CUDA(cudaMemcpyAsync(s.v_cache + at, v, rows * kv_width * 2, cudaMemcpyDefault, s.stream));
+    synchronize(s);
+  });
+}
+
+ei_status ei_session_adopt_history(ei_session* session, size_t length, uint32_t pending) {
+  return guarded([&] {
+    if (!session) throw std::invalid_argument("session is null");
+    ei_session& s = *session;
+    require_usable(s);
+    require_device(s);
+    if (length > s.capacity) throw LengthError("History exceeds session capacity");
+    if (pending >= s.model->config.vocab_size) throw std::invalid_argument("Token exceeds vocabulary");
+    Control control{};
+    control.context = int32_t(length);
+    control.pending = pending;
+    synchronize(s);
+    EI_CUDA(cudaMemcpyAsync(s.control, &control, sizeof(Control), cudaMemcpyHostToDevice, s.stream));
+    synchronize(s);
+    s.context = length;
+    s.bound = length;
+    s.history_ready = true;
+  });
+}
+
 ei_status ei_session_read_logits(ei_session* session, size_t rows, void* host_logits) {
   return guarded([&] {
     if (!session || !host_logits || !rows || rows > kMaxRows) throw std::invalid_argument("session, rows or output is invalid");

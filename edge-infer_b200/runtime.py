@@ -196,6 +196,15 @@ class Session:
     def launches_per_step(self, rows: int) -> int:
         return self._lib.ei_session_launches_per_step(self._handle, rows)
 
+    def write_kv(self, layer: int, first: int, k, v) -> None:
+        """Copies K / V rows (numpy uint16 BF16 arrays or torch tensors, [rows, kv_heads*head_dim]) into the cache."""
+        rows = k.shape[0]
+        abi.check(self._lib.ei_session_write_kv(self._handle, layer, first, rows, C.c_void_p(_pointer(k)),
+                                                C.c_void_p(_pointer(v))))
+
+    def adopt_history(self, length: int, pending: int) -> None:
+        abi.check(self._lib.ei_session_adopt_history(self._handle, length, int(pending)))
+
     def inject_failure(self, nth_launch: int = 0, completion: bool = False) -> None:
         abi.check(self._lib.ei_session_inject_failure(self._handle, nth_launch, 1 if completion else 0))
 

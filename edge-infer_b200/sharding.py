@@ -35,3 +35,40 @@ def throughput(total_count: float, slowest_ms: float) -> float:
     if slowest_ms <= 0:
         raise ValueError("elapsed time must be positive")
     return total_count / (slowest_ms * 1e-3)
+
+
+def plan_sessions(total_sessions: int, world: int, rank: int, stack: int, seed: int, shortest: int, longest: int):
+    """The sessions one rank serves and how it stacks them into forwards.
+
+    Every rank derives the same seeded prompt lengths (uniform in [shortest, longest]) for all sessions, takes its
+    shard, and groups its sessions into batches of `stack` (the last batch may be smaller) that are verified by
+    one forward each. Returns (ids, lengths, batches): ids of the owned sessions, their prompt lengths, and the
+    batches as lists of positions into `ids`."""
+    import numpy as np
+
+    if stack < 1 or shortest < 1 or longest < shortest:
+        raise ValueError("invalid session plan")
+    lengths = np.random.default_rng(seed).integers(shortest, longest + 1, size=total_sessions)
+    ids = list(session_shard(total_sessions, world, rank))
+    batches = [list(range(first, min(first + stack, len(ids)))) for first in range(0, len(ids), stack)]
+    return ids, [int(lengths[i]) for i in ids], batches
+
+
+def simulate_accepts(substituted, rows: int, steps: int, budget: int):
+    """Accept lengths of `steps` greedy verify steps whose drafts are the exact greedy continuation except where
+    `substituted[i]` is true (position i of the continuation was replaced by a random id). Acceptance then depends
+    on the substitution mask alone: a step at continuation offset i emits 1 + the number of leading unsubstituted
+    drafts among positions i+1 .. i+rows-1 (a random replacement equals the true token with probability 1 / vocab:
+    ignored). `budget` steps are run before the walk rewinds to offset 0, as the benchmark loop does.
+    Returns the list of emitted counts."""
+    emitted, done = [], 0
+    while done < steps:
+        offset = 0
+        for _ in range(min(steps - done, budget)):
+            count = 1
+            while count < rows and not substituted[offset + count]:
+                count += 1
+            emitted.append(count)
+            offset += count
+            done += 1
+    return emitted

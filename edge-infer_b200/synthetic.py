@@ -182,6 +182,11 @@ def corrupt_drafts(seed: int, continuation: np.ndarray, p: float, vocab: int) ->
     return np.where(replace, random_ids, continuation).astype(np.uint32)
 
 
+def substitution_mask(seed: int, length: int, p: float) -> np.ndarray:
+    """Which positions corrupt_drafts(seed, continuation of `length`, p, ...) replaces (the same generator)."""
+    return _rng(seed, "drafts").random(length) < p
+
+
 # The benchmark configurations' shapes.
 def qwen3_0_6b(**kw) -> Shape:
     return Shape(vocab_size=151936, n_layers=28, n_heads=16, n_kv_heads=8, hidden_size=1024, intermediate_size=3072,

@@ -280,6 +280,16 @@ ei_status ei_session_synchronize(ei_session* session);
 void* ei_session_stream(const ei_session* session);
 /* Copies K and V rows [0, context) of one layer to the host as BF16 ([context, kv_heads*head_dim]). */
 ei_status ei_session_read_kv(ei_session* session, size_t layer, void* host_k, void* host_v);
+/* Restores a history: copies `rows` K and V rows (BF16, [rows, kv_heads*head_dim], host or device memory) of one
+ * layer into cache rows [first, first + rows), on the session's stream, and waits. Together with
+ * ei_session_adopt_history it moves a session's state (read with ei_session_read_kv) into another session of the
+ * same model, or seeds a synthetic history for a benchmark. No counterpart in the reference (its KVCache is only
+ * ever filled by its own forward passes, runtime/include/inference.hpp:71-106). */
+ei_status ei_session_write_kv(ei_session* session, size_t layer, size_t first, size_t rows, const void* k,
+                              const void* v);
+/* Declares cache rows [0, length) valid and `pending` the next input token, as after a prefill of `length`
+ * tokens whose greedy continuation is `pending`. length <= capacity, pending < vocabulary. */
+ei_status ei_session_adopt_history(ei_session* session, size_t length, uint32_t pending);
 /* Copies the first `rows` rows of the session's borrowed logits (BF16 [rows, vocab]) to the host: row 0 after
  * prefill / decode, rows 0..rows-1 after a verify step. */
 ei_status ei_session_read_logits(ei_session* session, size_t rows, void* host_logits);

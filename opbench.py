@@ -8,8 +8,8 @@ Every case cycles over enough distinct operand sets to exceed L2 (126 MB), is re
 that host launch cost is excluded, and is timed with CUDA events. Prints one line per case:
 time per launch, algorithmic bytes, achieved GB/s and the fraction of the measured HBM peak.
 
-    python edge-infer_b200/opbench.py                       # full sweep
-    python edge-infer_b200/opbench.py --op awq --n 24576 --k 4096 --rows 9 --fused   # one case (for ncu)
+    python opbench.py                       # full sweep
+    python opbench.py --op awq --n 24576 --k 4096 --rows 9 --fused   # one case (for ncu)
 """
 from __future__ import annotations
 
@@ -18,7 +18,7 @@ import json
 import sys
 from pathlib import Path
 
-ROOT = Path(__file__).resolve().parents[1]
+ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 import __graft_entry__ as entry  # noqa: E402
 

@@ -374,14 +374,15 @@ class ReferenceCuda:
         if not self.handle:
             raise RuntimeError(self.lib.ref_last_error().decode())
 
-    def forward(self, tokens: Sequence[int]) -> Tuple[np.ndarray, np.ndarray]:
-        """Returns (BF16 logits as FP32 [rows, vocab], greedy tokens [rows])."""
+    def forward(self, tokens: Sequence[int], want_logits: bool = True) -> Tuple[Optional[np.ndarray], np.ndarray]:
+        """Returns (BF16 logits as FP32 [rows, vocab] or None, greedy tokens [rows])."""
         ids = np.ascontiguousarray(tokens, dtype=np.uint32)
-        logits = np.empty((len(ids), self.shape.vocab_size), dtype=np.uint16)
+        logits = np.empty((len(ids), self.shape.vocab_size), dtype=np.uint16) if want_logits else None
         greedy = np.empty(len(ids), dtype=np.uint32)
-        if self.lib.ref_cuda_forward(self.handle, _ptr(ids), len(ids), _ptr(logits), _ptr(greedy)):
+        if self.lib.ref_cuda_forward(self.handle, _ptr(ids), len(ids), _ptr(logits) if want_logits else None,
+                                     _ptr(greedy)):
             raise RuntimeError(self.lib.ref_last_error().decode())
-        return bf16_to_float(logits), greedy
+        return (bf16_to_float(logits) if want_logits else None), greedy
 
     def size(self) -> int:
         return self.lib.ref_cuda_size(self.handle)

@@ -415,3 +415,33 @@ def test_enqueue_refuses_steps_that_could_pass_the_capacity(cuda, package):
     last, _ = session.drain()
     assert np.array_equal(session.read_kv(0)[0][:context], kv[0][:context])   # the settled history is intact
     assert last.context == session.context_size() >= context
+
+
+def test_history_restored_into_another_session_continues_bit_exactly(cuda, package):
+    """K/V rows read from one session and written into a fresh session of the same model, with the context length
+    and pending token adopted, give the same verify results bit for bit - the state of a session is its KV rows,
+    its length and its pending token, nothing else."""
+    syn = package.synthetic
+    shape = shapes(package)["qwen3_awq"]
+    model = package.Model(shape, syn.make_model(shape, seed=9))
+    prompt = syn.make_prompt(9, 41, shape.vocab_size)
+    source = model.new_session(128, graph=True)
+    source.prefill(prompt)
+    pending = package.runtime.greedy_token(source.read_logits(1)[0])
+    copy = model.new_session(128, graph=True)
+    for layer in range(shape.n_layers):
+        k, v = source.read_kv(layer)
+        copy.write_kv(layer, 0, np.ascontiguousarray(k), np.ascontiguousarray(v))
+    copy.adopt_history(len(prompt), pending)
+    assert copy.context_size() == len(prompt)
+    drafts = [int(t) for t in syn.make_prompt(10, 8, shape.vocab_size)]
+    for step in range(3):
+        a = source.verify([pending] + drafts)
+        b = copy.verify([pending] + drafts)
+        assert a.targets == b.targets and a.emitted == b.emitted and a.context == b.context
+        assert np.array_equal(source.read_logits(9), copy.read_logits(9))
+        pending = a.tokens[-1]
+    with pytest.raises(package.abi.LengthError):
+        copy.write_kv(0, 120, np.zeros((9, 256), dtype=np.uint16), np.zeros((9, 256), dtype=np.uint16))
+    with pytest.raises(package.abi.LengthError):
+        copy.adopt_history(129, 0)

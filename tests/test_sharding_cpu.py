@@ -29,6 +29,9 @@ def worker(rank: int, world: int, port: int, results):
     try:
         package = entry.load_package()
         shard = package.sharding.session_shard(7, world, rank)
+        ids, lengths, batches = package.sharding.plan_sessions(7, world, rank, 3, 5, 256, 8192)
+        assert ids == list(shard) and len(lengths) == len(ids)
+        assert [i for batch in batches for i in batch] == list(range(len(ids))) and max(map(len, batches)) <= 3
         # each rank "emits" 10 tokens per owned session and takes (rank + 1) * 100 ms
         counts, times = package.sharding.aggregate(dist, torch, [10 * len(shard), len(shard)], [100.0 * (rank + 1), 1.0],
                                                    "cpu")
@@ -69,3 +72,29 @@ def test_two_gloo_ranks_reduce_like_the_benchmark():
     assert counts0 == counts1 == [70.0, 7.0]                       # summed over ranks
     assert times0 == times1 == [200.0, 1.0]                        # the slowest rank's time
     assert value0 == value1 == pytest.approx(70.0 / 0.2)           # whole-job tokens per second
+
+
+def test_session_plan_is_the_same_on_every_rank_and_acceptance_follows_the_mask():
+    import numpy as np
+
+    import __graft_entry__ as entry
+
+    sharding = entry.load_package().sharding
+    everything = sharding.plan_sessions(64, 1, 0, 3, 5, 256, 8192)
+    assert len(everything[0]) == 64 and min(everything[1]) >= 256 and max(everything[1]) <= 8192
+    assert len(everything[2]) == 22 and len(everything[2][-1]) == 1
+    seen = {}
+    for rank in range(4):
+        ids, lengths, batches = sharding.plan_sessions(64, 4, rank, 3, 5, 256, 8192)
+        assert len(ids) == 16 and [len(b) for b in batches] == [3, 3, 3, 3, 3, 1]
+        for session, length in zip(ids, lengths):
+            assert length == everything[1][session]               # the same seeded lengths on every rank
+            seen[session] = length
+    assert len(seen) == 64
+    mask = np.zeros(64, dtype=bool)
+    mask[[3, 4, 20]] = True
+    # offset 0: drafts 1,2 accepted, 3 substituted -> 3; offset 3: draft 4 substituted -> 1; offset 4: 5..8 fine -> 5
+    assert sharding.simulate_accepts(mask, 5, 3, 100) == [3, 1, 5]
+    assert sharding.simulate_accepts(mask, 5, 4, 2) == [3, 1, 3, 1]                # rewinds after `budget` steps
+    with pytest.raises(ValueError):
+        sharding.plan_sessions(4, 1, 0, 0, 1, 1, 2)
