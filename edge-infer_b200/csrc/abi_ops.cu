@@ -16,44 +16,68 @@ thread_local std::string g_last_error;
 
 namespace {
 
-int checked_int(size_t value) {
-  if (!value || value > size_t(std::numeric_limits<int>::max()))
-    throw std::invalid_argument("CUDA execution extent must be positive and fit int");
-  return int(value);
+// ---- argument checks ------------------------------------------------------------------------------------
+// Every operator rejects a malformed call with std::invalid_argument (EI_INVALID_ARGUMENT across the ABI)
+// before it writes anything, as the reference's operators do (operators/src/cuda/execution.cu:23-58).
+
+[[noreturn]] void reject(const std::string& what) { throw std::invalid_argument(what); }
+
+// Extents cross the ABI as size_t and index the kernels as int.
+int kernel_extent(size_t extent, const char* name) {
+  if (extent < 1 || extent > size_t(std::numeric_limits<int>::max()))
+    reject(std::string(name) + " must lie between 1 and 2^31 - 1");
+  return int(extent);
 }
 
 template <typename View>
-size_t numel(const View& v) {
-  size_t count = 1;
-  for (size_t extent : v.shape) count *= extent;
-  return count;
+constexpr int rank_of(const View& v) {
+  return int(sizeof(v.shape) / sizeof(v.shape[0]));
 }
 
 template <typename View>
-bool contiguous(const View& v) {
-  if (!numel(v)) return true;
-  size_t expected = 1;
-  constexpr size_t rank = sizeof(v.shape) / sizeof(v.shape[0]);
-  for (size_t axis = rank; axis-- > 0;) {
-    if (v.shape[axis] != 1 && v.stride[axis] != expected) return false;
-    expected *= v.shape[axis];
+size_t elements(const View& v) {
+  size_t product = 1;
+  for (int axis = 0; axis < rank_of(v); ++axis) product *= v.shape[axis];
+  return product;
+}
+
+// Packed: walking the axes from the innermost outwards, each axis steps over exactly what lies inside it.
+// An axis of extent 1 is never stepped along, so its stride is not looked at.
+template <typename View>
+bool packed(const View& v) {
+  size_t step = 1;
+  for (int axis = rank_of(v) - 1; axis >= 0; --axis) {
+    if (v.shape[axis] > 1 && v.stride[axis] != step) return false;
+    step *= v.shape[axis];
   }
   return true;
 }
 
+// An operand the kernels index as one dense array.
 template <typename View>
-void require_dense(const View& v) {
-  if (!v.data || !numel(v) || !contiguous(v))
-    throw std::invalid_argument("CUDA execution requires a nonempty contiguous view");
+void expect_packed(const View& v, const char* name) {
+  if (v.data == nullptr) reject(std::string(name) + " has no storage");
+  if (elements(v) == 0) reject(std::string(name) + " is empty");
+  if (!packed(v)) reject(std::string(name) + " must be a packed row-major view");
 }
 
-void require_heads(const ei_view3& v) {
-  if (!v.data || !numel(v) || v.stride[2] != 1 || v.stride[1] != v.shape[2] ||
-      v.stride[0] < v.shape[1] * v.shape[2])
-    throw std::invalid_argument("CUDA attention/RoPE requires contiguous heads within each row");
-  checked_int(v.shape[0]);
-  checked_int(v.shape[1]);
-  checked_int(v.shape[2]);
+// [rows, heads, width] with every head row packed and the heads of a row adjacent; rows may be strided
+// (a slice of a wider projection output, a window of a cache).
+void expect_head_rows(const ei_view3& v, const char* name) {
+  if (v.data == nullptr || elements(v) == 0) reject(std::string(name) + " has no storage or is empty");
+  const bool heads_adjacent = v.stride[2] == 1 && v.stride[1] == v.shape[2];
+  const bool rows_disjoint = v.stride[0] >= v.shape[1] * v.shape[2];
+  if (!heads_adjacent || !rows_disjoint) reject(std::string(name) + " must keep the heads of a row packed and adjacent");
+  kernel_extent(v.shape[0], "rows");
+  kernel_extent(v.shape[1], "heads");
+  kernel_extent(v.shape[2], "head width");
+}
+
+// A bias is optional; when present it has one packed value per output feature.
+void expect_bias(const ei_view1& bias, size_t outputs, const char* name) {
+  if (bias.data == nullptr) return;
+  if (bias.shape[0] != outputs) reject(std::string(name) + " must have one value per output feature");
+  if (outputs > 1 && bias.stride[0] != 1) reject(std::string(name) + " must be packed");
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -102,24 +126,27 @@ ei_status ei_prepare_execution_context(void* stream, ei_context* out) {
 
 ei_status ei_prepare_dense_bf16(ei_view2 weight, ei_view1 bias, ei_dense_weight* out) {
   return guarded([&] {
-    const int input = checked_int(weight.shape[0]), output = checked_int(weight.shape[1]);
-    if (!out || !weight.data ||
-        (bias.data && (bias.shape[0] != weight.shape[1] || (bias.shape[0] != 1 && bias.stride[0] != 1))))
-      throw std::invalid_argument("Invalid direct dense linear weight or bias");
+    // `weight` is the logical [inputs, outputs] matrix; what matters to the kernels is along which axis its
+    // storage is contiguous.
+    if (out == nullptr) reject("dense weight output is null");
+    if (weight.data == nullptr) reject("dense weight has no storage");
     ei_dense_weight prepared{};
     prepared.data = weight.data;
-    prepared.bias = bias.data;
-    prepared.input_features = input;
-    prepared.output_features = output;
-    if (weight.stride[0] == 1 && weight.stride[1] >= weight.shape[0]) {
+    prepared.input_features = kernel_extent(weight.shape[0], "input features");
+    prepared.output_features = kernel_extent(weight.shape[1], "output features");
+    const bool inputs_contiguous = weight.stride[0] == 1 && weight.stride[1] >= weight.shape[0];   // [out, in] storage
+    const bool outputs_contiguous = weight.stride[1] == 1 && weight.stride[0] >= weight.shape[1];  // [in, out] storage
+    if (inputs_contiguous) {
       prepared.operation = 1;
-      prepared.leading_dimension = checked_int(weight.stride[1]);
-    } else if (weight.stride[1] == 1 && weight.stride[0] >= weight.shape[1]) {
+      prepared.leading_dimension = kernel_extent(weight.stride[1], "weight pitch");
+    } else if (outputs_contiguous) {
       prepared.operation = 0;
-      prepared.leading_dimension = checked_int(weight.stride[0]);
+      prepared.leading_dimension = kernel_extent(weight.stride[0], "weight pitch");
     } else {
-      throw std::invalid_argument("Direct dense linear supports row-major or transposed matrix views");
+      reject("a dense weight must be contiguous along its input or its output axis");
     }
+    expect_bias(bias, weight.shape[1], "dense bias");
+    prepared.bias = bias.data;
     *out = prepared;
   });
 }
@@ -127,18 +154,30 @@ ei_status ei_prepare_dense_bf16(ei_view2 weight, ei_view1 bias, ei_dense_weight*
 ei_status ei_prepare_awq_bf16(ei_view2 qweight, ei_view2 scales, ei_view2 zeros, size_t group_size,
                               size_t input_features, ei_view1 bias, ei_awq_weight* out) {
   return guarded([&] {
-    require_dense(qweight);
-    require_dense(scales);
-    require_dense(zeros);
-    const int input = checked_int(input_features), output = checked_int(qweight.shape[0]);
-    const int group = checked_int(group_size), padded = checked_int(scales.shape[1]);
-    if (!out || input_features % group_size || qweight.shape[1] != (input_features + 7) / 8 ||
-        scales.shape[0] != qweight.shape[0] || scales.shape[1] < input_features / group_size ||
-        zeros.shape[0] != qweight.shape[0] || zeros.shape[1] != (input_features / group_size + 7) / 8 ||
-        (bias.data && (bias.shape[0] != qweight.shape[0] || (bias.shape[0] != 1 && bias.stride[0] != 1))))
-      throw std::invalid_argument("Direct AWQ linear requires N-major packed weights, scales and zeros");
-    *out = ei_awq_weight{static_cast<const int32_t*>(qweight.data), scales.data,
-                         static_cast<const int32_t*>(zeros.data), bias.data, input, output, group, padded};
+    // N-major packing of the reference (operators/src/cuda/kernels/awq_gemv_gemm.cu:591-599): one row per output
+    // feature in all three arrays; eight nibbles per word, one scale per group (the row may be padded), eight
+    // zero points per word.
+    if (out == nullptr) reject("AWQ weight output is null");
+    expect_packed(qweight, "AWQ packed weights");
+    expect_packed(scales, "AWQ scales");
+    expect_packed(zeros, "AWQ zero points");
+    ei_awq_weight prepared{};
+    prepared.input_features = kernel_extent(input_features, "input features");
+    prepared.output_features = kernel_extent(qweight.shape[0], "output features");
+    prepared.group_size = kernel_extent(group_size, "group size");
+    prepared.padded_groups = kernel_extent(scales.shape[1], "scale row length");
+    if (input_features % group_size != 0) reject("AWQ input features must be a whole number of groups");
+    const size_t outputs = qweight.shape[0], groups = input_features / group_size;
+    if (qweight.shape[1] != (input_features + 7) / 8) reject("AWQ packed weights must hold eight inputs per word");
+    if (scales.shape[0] != outputs || scales.shape[1] < groups) reject("AWQ scales must cover every output and group");
+    if (zeros.shape[0] != outputs || zeros.shape[1] != (groups + 7) / 8)
+      reject("AWQ zero points must hold eight groups per word for every output");
+    expect_bias(bias, outputs, "AWQ bias");
+    prepared.qweight = static_cast<const int32_t*>(qweight.data);
+    prepared.scales = scales.data;
+    prepared.zeros = static_cast<const int32_t*>(zeros.data);
+    prepared.bias = bias.data;
+    *out = prepared;
   });
 }
 
@@ -152,9 +191,9 @@ ei_status ei_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_dense_w
                          void* scratch, size_t scratch_bytes) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_dense(input);
-    require_dense(output);
-    checked_int(input.shape[0]);
+    expect_packed(input, "input");
+    expect_packed(output, "output");
+    kernel_extent(input.shape[0], "rows");
     if (!weight || !weight->data || input.shape[1] != size_t(weight->input_features) ||
         output.shape[0] != input.shape[0] || output.shape[1] != size_t(weight->output_features))
       throw std::invalid_argument("Direct dense linear input/output dimensions or handle are invalid");
@@ -201,9 +240,9 @@ ei_status ei_awq_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_awq
                              void* scratch, size_t scratch_bytes) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_dense(input);
-    require_dense(output);
-    checked_int(input.shape[0]);
+    expect_packed(input, "input");
+    expect_packed(output, "output");
+    kernel_extent(input.shape[0], "rows");
     if (!weight || !weight->qweight || !weight->scales || !weight->zeros ||
         input.shape[1] != size_t(weight->input_features) || output.shape[0] != input.shape[0] ||
         output.shape[1] != size_t(weight->output_features))
@@ -253,8 +292,8 @@ ei_status ei_awq_gate_up_silu_bf16(const ei_context* ctx, ei_view2 input, const 
                                    ei_view2 output) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_dense(input);
-    require_dense(output);
+    expect_packed(input, "input");
+    expect_packed(output, "output");
     if (!weight || !weight->qweight || !weight->scales || !weight->zeros || weight->output_features % 2 ||
         input.shape[1] != size_t(weight->input_features) || output.shape[0] != input.shape[0] ||
         output.shape[1] != size_t(weight->output_features / 2))
@@ -289,7 +328,7 @@ ei_status ei_add_bf16(const ei_context* ctx, ei_array a, ei_array b, ei_array ou
     if (!a.size) return;
     if (!a.data || !b.data || !out.data) throw std::invalid_argument("Add operator: null storage");
     launch_add(static_cast<const bf16*>(a.data), static_cast<const bf16*>(b.data), static_cast<bf16*>(out.data),
-               a.size, stream);
+               a.size, ctx->multiprocessors, stream);
   });
 }
 
@@ -302,7 +341,7 @@ ei_status ei_silu_multiply_bf16(const ei_context* ctx, ei_array gate, ei_array u
     if (gate.size > size_t(std::numeric_limits<int>::max()))
       throw std::runtime_error("SiLU multiply CUDA view extent exceeds the kernel index range");
     launch_silu_multiply(static_cast<const bf16*>(gate.data), static_cast<const bf16*>(up.data),
-                         static_cast<bf16*>(out.data), gate.size, stream);
+                         static_cast<bf16*>(out.data), gate.size, ctx->multiprocessors, stream);
   });
 }
 
@@ -327,9 +366,9 @@ ei_status ei_rms_norm_bf16(const ei_context* ctx, ei_array input, ei_array weigh
 ei_status ei_gather_bf16(const ei_context* ctx, ei_view1 ids, ei_view2 table, ei_view2 out) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_dense(ids);
-    require_dense(table);
-    require_dense(out);
+    expect_packed(ids, "token ids");
+    expect_packed(table, "embedding table");
+    expect_packed(out, "output");
     if (out.shape[0] != ids.shape[0] || out.shape[1] != table.shape[1])
       throw std::invalid_argument("Direct gather input/output shapes differ");
     launch_gather(static_cast<const uint32_t*>(ids.data), static_cast<const bf16*>(table.data),
@@ -342,15 +381,16 @@ ei_status ei_rope_precomputed_bf16(const ei_context* ctx, ei_view3 input, ei_vie
                                    const size_t* offsets, const int* pingpong) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_heads(input);
-    require_dense(table);
+    expect_head_rows(input, "RoPE input");
+    expect_packed(table, "RoPE table");
     if (table.shape[1] != input.shape[2] || input.shape[2] % 2 ||
         input.shape[2] / 2 > size_t(ctx->max_threads_per_block ? ctx->max_threads_per_block : 1024))
       throw std::invalid_argument("Direct cached RoPE has incompatible cache or offsets");
     if (!offsets && (offset > table.shape[0] || input.shape[0] > table.shape[0] - offset))
       throw std::out_of_range("Direct cached RoPE positions exceed table capacity");
     launch_rope(static_cast<bf16*>(input.data), input.shape[0], input.shape[1], input.shape[2], input.stride[0],
-                static_cast<const float*>(table.data), table.stride[0], offset, offsets, pingpong, stream);
+                static_cast<const float*>(table.data), table.stride[0], offset, offsets, pingpong, ctx->multiprocessors,
+                stream);
   });
 }
 
@@ -372,8 +412,8 @@ ei_status ei_store_kv_bf16(const ei_context* ctx, ei_view2 source, ei_view2 capa
                            const size_t* device_offset) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_dense(source);
-    require_dense(capacity);
+    expect_packed(source, "KV source");
+    expect_packed(capacity, "KV cache");
     if (source.shape[1] != capacity.shape[1] || offset > capacity.shape[0] ||
         source.shape[0] > capacity.shape[0] - offset)
       throw std::invalid_argument("Direct KV store source or offset exceeds cache capacity");
@@ -390,14 +430,17 @@ size_t ei_attention_scratch_bytes(size_t q_rows, size_t query_heads, size_t head
 static void run_attention(const ei_context* ctx, ei_view3 q, ei_view3 k, ei_view3 v, ei_view3 out, size_t offset,
                           const int32_t* device_offset, void* scratch, size_t scratch_bytes) {
   cudaStream_t stream = stream_of(ctx);
-  require_heads(q);
-  require_heads(k);
-  require_heads(v);
-  require_heads(out);
-  if (k.shape[0] != v.shape[0] || k.shape[1] != v.shape[1] || k.shape[2] != v.shape[2] ||
-      q.shape[0] != out.shape[0] || q.shape[1] != out.shape[1] || q.shape[2] != out.shape[2] ||
-      q.shape[2] != k.shape[2] || q.shape[1] % k.shape[1] || q.shape[2] > 1024)
-    throw std::invalid_argument("CUDA attention query, KV and output shapes are incompatible");
+  expect_head_rows(q, "attention queries");
+  expect_head_rows(k, "attention keys");
+  expect_head_rows(v, "attention values");
+  expect_head_rows(out, "attention output");
+  auto same_shape = [](const ei_view3& a, const ei_view3& b) {
+    return a.shape[0] == b.shape[0] && a.shape[1] == b.shape[1] && a.shape[2] == b.shape[2];
+  };
+  if (!same_shape(k, v)) reject("attention keys and values must have one shape");
+  if (!same_shape(q, out)) reject("attention output must have the queries' shape");
+  if (q.shape[2] != k.shape[2]) reject("attention queries and keys must share the head width");
+  if (q.shape[1] % k.shape[1] != 0) reject("query heads must be a whole multiple of KV heads");
   if (!device_offset && (offset > k.shape[0] || q.shape[0] > k.shape[0] - offset))
     throw std::invalid_argument("Direct prefill attention offset exceeds live KV extent");
   const size_t group = q.shape[1] / k.shape[1];
@@ -500,21 +543,21 @@ ei_status ei_attention_prefill_static_bf16(const ei_context* ctx, ei_view3 q, ei
 size_t ei_sample_scratch_bytes(size_t rows, size_t vocabulary) {
   (void)rows;
   (void)vocabulary;
-  return size_t(148) * 16 * (sizeof(float) + sizeof(int));  // partial (value, index) per block and row
+  return size_t(kSampleMaxParts) * 16 * (sizeof(float) + sizeof(int));  // partial (value, index) per block and row
 }
 
 ei_status ei_sample_greedy_bf16(const ei_context* ctx, ei_view2 logits, ei_view1 tokens, void* scratch,
                                 size_t scratch_bytes) {
   return guarded([&] {
     cudaStream_t stream = stream_of(ctx);
-    require_dense(logits);
-    require_dense(tokens);
-    checked_int(logits.shape[1]);
+    expect_packed(logits, "logits");
+    expect_packed(tokens, "tokens");
+    kernel_extent(logits.shape[1], "vocabulary");
     if (tokens.shape[0] != logits.shape[0] || !scratch || scratch_bytes < ei_sample_scratch_bytes(0, 0))
       throw std::invalid_argument("Direct sampling parameters, plan or output capacities are invalid");
-    const int blocks = std::min(148, sample_partial_blocks(logits.shape[1], ctx->multiprocessors));
+    const int blocks = std::min(kSampleMaxParts, sample_partial_blocks(logits.shape[1], ctx->multiprocessors));
     float* best_value = static_cast<float*>(scratch);
-    int* best_index = reinterpret_cast<int*>(best_value + 148 * 16);
+    int* best_index = reinterpret_cast<int*>(best_value + kSampleMaxParts * 16);
     for_row_groups(logits.shape[0], [&](size_t first, size_t rows) {
       launch_argmax_partials(static_cast<const bf16*>(logits.data) + first * logits.stride[0], rows, logits.shape[1],
                              logits.stride[0], best_value, best_index, blocks, stream, false);

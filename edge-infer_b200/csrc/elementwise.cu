@@ -66,11 +66,27 @@ __global__ void silu_multiply_kernel(const bf16* gate, const bf16* up, bf16* out
     out[i] = __float2bfloat16_rn(silu_multiply_value(__bfloat162float(gate[i]), __bfloat162float(up[i])));
 }
 
-__global__ void gather_kernel(const uint32_t* ids, const bf16* table, bf16* out, size_t count, size_t width,
-                              size_t vocabulary) {
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x) {
-    const uint32_t token = ids[i / width];
-    out[i] = token < vocabulary ? table[size_t(token) * width + i % width] : __float2bfloat16_rn(0.0f);
+// ---- the direct operators' copy-shaped kernels: 16 bytes per thread where the operands allow it ------------
+
+// Embedding lookup: row r of `out` is row ids[r] of `table`, or zeros for an id outside the table. A thread moves
+// one 16-byte piece (8 values) of a row; `pieces` = pieces per row (rows are 16-byte aligned multiples of 8 values).
+__global__ void gather_rows_vec_kernel(const uint32_t* ids, const uint4* table, uint4* out, size_t rows, size_t pieces,
+                                       size_t vocabulary) {
+  const size_t total = rows * pieces;
+  for (size_t at = size_t(blockIdx.x) * blockDim.x + threadIdx.x; at < total; at += size_t(gridDim.x) * blockDim.x) {
+    const size_t row = at / pieces, piece = at - row * pieces;
+    const uint32_t token = ids[row];
+    out[at] = token < vocabulary ? table[size_t(token) * pieces + piece] : make_uint4(0, 0, 0, 0);
+  }
+}
+// Any width or alignment: one value per thread.
+__global__ void gather_rows_kernel(const uint32_t* ids, const bf16* table, bf16* out, size_t rows, size_t width,
+                                   size_t vocabulary) {
+  const size_t total = rows * width;
+  for (size_t at = size_t(blockIdx.x) * blockDim.x + threadIdx.x; at < total; at += size_t(gridDim.x) * blockDim.x) {
+    const size_t row = at / width, column = at - row * width;
+    const uint32_t token = ids[row];
+    out[at] = token < vocabulary ? table[size_t(token) * width + column] : __float2bfloat16_rn(0.0f);
   }
 }
 
@@ -82,26 +98,35 @@ __device__ __forceinline__ void rotate_pair(float x, float y, float sine, float 
   second = round_bf16(round_bf16(x * sine) + round_bf16(y * cosine));
 }
 
-__global__ void rope_kernel(bf16* data, size_t row_stride, size_t head_dim, const float* table,
-                            size_t table_stride, size_t offset, const size_t* offsets, const int* pingpong) {
-  const size_t pair = threadIdx.x, half = head_dim / 2;
-  if (pair >= half) return;
-  const size_t position = blockIdx.x + (offsets ? offsets[pingpong ? *pingpong : 0] : offset);
-  bf16* head = data + size_t(blockIdx.x) * row_stride + size_t(blockIdx.y) * head_dim;
-  float first, second;
-  rotate_pair(__bfloat162float(head[pair]), __bfloat162float(head[pair + half]),
-              table[position * table_stride + 2 * pair], table[position * table_stride + 2 * pair + 1], first,
-              second);
-  head[pair] = __float2bfloat16_rn(first);
-  head[pair + half] = __float2bfloat16_rn(second);
+// Half-split RoPE in place over [rows, heads, width]: a thread owns rotation pair `pair` of one head row,
+// i.e. elements pair and pair + width / 2; the table row of position p holds (sine, cosine) of pair i at
+// [2 i, 2 i + 1]. The first row's position comes from the host or, in a captured graph, from device memory.
+__global__ void rope_pairs_kernel(bf16* data, size_t rows, size_t heads, size_t width, size_t row_stride,
+                                  const float* table, size_t table_stride, size_t host_offset,
+                                  const size_t* device_offsets, const int* which_offset) {
+  const size_t half = width / 2, total = rows * heads * half;
+  const size_t first_position = device_offsets ? device_offsets[which_offset ? *which_offset : 0] : host_offset;
+  for (size_t at = size_t(blockIdx.x) * blockDim.x + threadIdx.x; at < total; at += size_t(gridDim.x) * blockDim.x) {
+    const size_t pair = at % half, head = (at / half) % heads, row = at / (half * heads);
+    bf16* values = data + row * row_stride + head * width;
+    const float2 trig = *reinterpret_cast<const float2*>(table + (first_position + row) * table_stride + 2 * pair);
+    float first, second;
+    rotate_pair(__bfloat162float(values[pair]), __bfloat162float(values[pair + half]), trig.x, trig.y, first, second);
+    values[pair] = __float2bfloat16_rn(first);
+    values[pair + half] = __float2bfloat16_rn(second);
+  }
 }
 
-__global__ void store_kv_kernel(const bf16* source, bf16* cache, size_t count, size_t rows, size_t width,
-                                size_t capacity, size_t offset, const size_t* device_offset) {
-  const size_t start_row = device_offset ? *device_offset : offset;
-  if (start_row > capacity || rows > capacity - start_row) return;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
-    cache[start_row * width + i] = source[i];
+// KV append: `rows` packed rows of `width` values land at cache row `first` (host value or device word). A
+// request that would pass the capacity writes nothing.
+template <typename Piece>
+__global__ void append_rows_kernel(const Piece* source, Piece* cache, size_t pieces, size_t pieces_per_row, size_t rows,
+                                   size_t capacity, size_t host_first, const size_t* device_first) {
+  const size_t first = device_first ? *device_first : host_first;
+  if (first > capacity || rows > capacity - first) return;
+  Piece* target = cache + first * pieces_per_row;
+  for (size_t at = size_t(blockIdx.x) * blockDim.x + threadIdx.x; at < pieces; at += size_t(gridDim.x) * blockDim.x)
+    target[at] = source[at];
 }
 
 __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedParams p) {
@@ -390,35 +415,53 @@ void launch_rms_norm(const bf16* in, const bf16* weight, bf16* out, size_t rows,
          int(width), eps);
 }
 
-void launch_add(const bf16* a, const bf16* b, bf16* out, size_t count, cudaStream_t stream) {
-  add_kernel<<<blocks_for(count, 148), 256, 0, stream>>>(a, b, out, count);
+void launch_add(const bf16* a, const bf16* b, bf16* out, size_t count, int multiprocessors, cudaStream_t stream) {
+  add_kernel<<<blocks_for(count, multiprocessors), 256, 0, stream>>>(a, b, out, count);
   check_launch();
 }
 
-void launch_silu_multiply(const bf16* gate, const bf16* up, bf16* out, size_t count, cudaStream_t stream) {
-  silu_multiply_kernel<<<blocks_for(count, 148), 256, 0, stream>>>(gate, up, out, count);
+void launch_silu_multiply(const bf16* gate, const bf16* up, bf16* out, size_t count, int multiprocessors,
+                          cudaStream_t stream) {
+  silu_multiply_kernel<<<blocks_for(count, multiprocessors), 256, 0, stream>>>(gate, up, out, count);
   check_launch();
 }
+
+namespace {
+bool sixteen_byte_aligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace
 
 void launch_gather(const uint32_t* ids, const bf16* table, bf16* out, size_t rows, size_t width,
                    size_t vocabulary, int multiprocessors, cudaStream_t stream) {
-  gather_kernel<<<blocks_for(rows * width, multiprocessors), 256, 0, stream>>>(ids, table, out, rows * width,
-                                                                             width, vocabulary);
+  if (width % 8 == 0 && sixteen_byte_aligned(table) && sixteen_byte_aligned(out)) {
+    const size_t pieces = width / 8;
+    gather_rows_vec_kernel<<<blocks_for(rows * pieces, multiprocessors), 256, 0, stream>>>(
+        ids, reinterpret_cast<const uint4*>(table), reinterpret_cast<uint4*>(out), rows, pieces, vocabulary);
+  } else {
+    gather_rows_kernel<<<blocks_for(rows * width, multiprocessors), 256, 0, stream>>>(ids, table, out, rows, width,
+                                                                                   vocabulary);
+  }
   check_launch();
 }
 
 void launch_rope(bf16* data, size_t rows, size_t heads, size_t head_dim, size_t row_stride, const float* table,
-                 size_t table_stride, size_t offset, const size_t* offsets, const int* pingpong,
+                 size_t table_stride, size_t offset, const size_t* offsets, const int* pingpong, int multiprocessors,
                  cudaStream_t stream) {
-  rope_kernel<<<dim3(unsigned(rows), unsigned(heads)), unsigned(head_dim / 2), 0, stream>>>(
-      data, row_stride, head_dim, table, table_stride, offset, offsets, pingpong);
+  rope_pairs_kernel<<<blocks_for(rows * heads * (head_dim / 2), multiprocessors), 256, 0, stream>>>(
+      data, rows, heads, head_dim, row_stride, table, table_stride, offset, offsets, pingpong);
   check_launch();
 }
 
 void launch_store_kv(const bf16* source, bf16* cache, size_t rows, size_t width, size_t capacity, size_t offset,
                      const size_t* device_offset, int multiprocessors, cudaStream_t stream) {
-  store_kv_kernel<<<blocks_for(rows * width, multiprocessors), 256, 0, stream>>>(
-      source, cache, rows * width, rows, width, capacity, offset, device_offset);
+  if (width % 8 == 0 && sixteen_byte_aligned(source) && sixteen_byte_aligned(cache)) {
+    const size_t per_row = width / 8;
+    append_rows_kernel<uint4><<<blocks_for(rows * per_row, multiprocessors), 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(source), reinterpret_cast<uint4*>(cache), rows * per_row, per_row, rows, capacity,
+        offset, device_offset);
+  } else {
+    append_rows_kernel<bf16><<<blocks_for(rows * width, multiprocessors), 256, 0, stream>>>(
+        source, cache, rows * width, width, rows, capacity, offset, device_offset);
+  }
   check_launch();
 }
 

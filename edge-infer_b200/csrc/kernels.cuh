@@ -19,13 +19,14 @@ struct Control {
 // ---- elementwise.cu ----
 void launch_rms_norm(const bf16* in, const bf16* weight, bf16* out, size_t rows, size_t width, float eps,
                      cudaStream_t stream, bool pdl);
-void launch_add(const bf16* a, const bf16* b, bf16* out, size_t count, cudaStream_t stream);
-void launch_silu_multiply(const bf16* gate, const bf16* up, bf16* out, size_t count, cudaStream_t stream);
+void launch_add(const bf16* a, const bf16* b, bf16* out, size_t count, int multiprocessors, cudaStream_t stream);
+void launch_silu_multiply(const bf16* gate, const bf16* up, bf16* out, size_t count, int multiprocessors,
+                          cudaStream_t stream);
 void launch_gather(const uint32_t* ids, const bf16* table, bf16* out, size_t rows, size_t width,
                    size_t vocabulary, int multiprocessors, cudaStream_t stream);
 void launch_rope(bf16* data, size_t rows, size_t heads, size_t head_dim, size_t row_stride,
                  const float* table, size_t table_stride, size_t offset, const size_t* offsets,
-                 const int* pingpong, cudaStream_t stream);
+                 const int* pingpong, int multiprocessors, cudaStream_t stream);
 void launch_store_kv(const bf16* source, bf16* cache, size_t rows, size_t width, size_t capacity,
                      size_t offset, const size_t* device_offset, int multiprocessors, cudaStream_t stream);
 
@@ -109,7 +110,9 @@ size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length);
 void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);
 
 // ---- sampling.cu ----
-// Per-row argmax partials of logits [rows, vocab] into best_value / best_index [blocks, 16].
+// Per-row argmax partials of logits [rows, vocab] into best_value / best_index [blocks, 16]; at most
+// kSampleMaxParts blocks (the size every partial buffer is given).
+constexpr int kSampleMaxParts = 256;
 int sample_partial_blocks(size_t vocabulary, int multiprocessors);
 void launch_argmax_partials(const bf16* logits, size_t rows, size_t vocab, size_t row_stride,
                             float* best_value, int* best_index, int blocks, cudaStream_t stream, bool pdl);

@@ -102,7 +102,7 @@ struct ei_model {
   std::vector<Layer> layers;
   float* rope_table = nullptr;
   size_t weight_bytes = 0;
-  int multiprocessors = 148;
+  int multiprocessors = 1;  // queried at creation
   size_t smem_limit = 227 * 1024;
 };
 
@@ -541,7 +541,7 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
       run_linear(s, m.lm_head, s.normed, rows, kEpiArgmax, logits, int(c.vocab_size), pdl, &parts);
     } else {
       run_generic(s, m.lm_head, s.normed, rows, logits, pdl);
-      parts = std::min(148, sample_partial_blocks(c.vocab_size, m.multiprocessors));
+      parts = std::min(kSampleMaxParts, sample_partial_blocks(c.vocab_size, m.multiprocessors));
       tick(s);
       launch_argmax_partials(logits, rows, c.vocab_size, c.vocab_size, s.best_value, s.best_index, parts, s.stream, pdl);
     }
@@ -690,7 +690,7 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
     run_linear(lead, m.lm_head, lead.normed, total, kEpiArgmax, lead.logits, int(c.vocab_size), pdl, &parts);
   } else {
     run_generic(lead, m.lm_head, lead.normed, total, lead.logits, pdl);
-    parts = std::min(148, sample_partial_blocks(c.vocab_size, m.multiprocessors));
+    parts = std::min(kSampleMaxParts, sample_partial_blocks(c.vocab_size, m.multiprocessors));
     tick(lead);
     launch_argmax_partials(lead.logits, total, c.vocab_size, c.vocab_size, lead.best_value, lead.best_index, parts,
                            lead.stream, pdl);
@@ -890,7 +890,8 @@ ei_status ei_session_create(ei_model* model, size_t capacity, int graph, ei_sess
     const size_t o_projection = take(kMaxRows * H * 2), o_logits = take(kMaxRows * V * 2);
     const size_t o_partial = take(size_t(16) * kMaxRows * H * sizeof(float));
     const size_t o_scratch = take(attention_scratch_bytes(kMaxRows, c.n_heads, capacity));
-    const size_t o_best_value = take(size_t(256) * 16 * sizeof(float)), o_best_index = take(size_t(256) * 16 * sizeof(int));
+    const size_t o_best_value = take(size_t(kSampleMaxParts) * 16 * sizeof(float));
+    const size_t o_best_index = take(size_t(kSampleMaxParts) * 16 * sizeof(int));
     const size_t o_tokens = take(kMaxRows * 4), o_step = take(kMaxRows * 4), o_targets = take(kMaxRows * 4);
     const size_t o_control = take(sizeof(Control)), o_source = take(sizeof(DraftSource));
     const size_t o_sink = take(sizeof(TokenSink));

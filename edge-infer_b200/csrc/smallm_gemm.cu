@@ -105,7 +105,8 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
   int per_warp = (units + kGemmWarps - 1) / kGemmWarps;
   if (per_warp == 3) per_warp = 4;
   const int chunks = pair ? N / 16 : N / 8;
-  const int groups = std::max(1, std::min(multiprocessors / ks, chunks));
+  int groups = std::max(1, std::min(multiprocessors / ks, chunks));
+  if (epilogue == kEpiArgmax) groups = std::min(groups, 256);  // one argmax partial per block: the buffers hold 256
   size_t smem = kPartBytes + size_t(units) * unit_k * 16 * (plan.high ? 2 : 1);
   if (awq) {
     if (epilogue == kEpiArgmax) return plan;  // the vocabulary head is a dense matrix
