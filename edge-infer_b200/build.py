@@ -17,7 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libedge_infer_b200.so"
-SOURCES = ["abi_ops.cu", "smallm_gemm.cu", "elementwise.cu", "attention.cu", "sampling.cu", "runtime.cu"]
+SOURCES = ["abi_ops.cu", "smallm_gemm.cu", "prompt_gemm.cu", "elementwise.cu", "attention.cu", "sampling.cu", "runtime.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -200,6 +200,17 @@ ei_status ei_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_dense_w
     const int K = weight->input_features, N = weight->output_features;
     const bool fast_layout = weight->operation == 1 && aligned16(weight->data) && weight->leading_dimension % 8 == 0 &&
                              aligned16(input.data);
+    // Many rows: one pass on the tensor cores instead of one weight stream per 16 rows.
+    if (input.shape[0] > kPromptMinRows && fast_layout &&
+        prompt_gemm_eligible(false, 0, N, K, input.data, K, output.data, N)) {
+      GemmParams p{};
+      p.x = static_cast<const bf16*>(input.data); p.x_stride = K; p.M = int(input.shape[0]); p.K = K; p.N = N;
+      p.w = static_cast<const bf16*>(weight->data); p.ldw = weight->leading_dimension;
+      p.bias = static_cast<const bf16*>(weight->bias);
+      p.out = static_cast<bf16*>(output.data); p.out_stride = N;
+      launch_prompt_gemm(false, p, stream, false);
+      return;
+    }
     for_row_groups(input.shape[0], [&](size_t first, size_t rows) {
       const bf16* x = static_cast<const bf16*>(input.data) + first * K;
       bf16* out = static_cast<bf16*>(output.data) + first * N;
@@ -249,6 +260,20 @@ ei_status ei_awq_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_awq
       throw std::invalid_argument("Direct AWQ linear input/output dimensions are invalid");
     const int K = weight->input_features, N = weight->output_features;
     const bool fast_layout = weight->group_size == 128 && aligned16(weight->qweight) && aligned16(input.data);
+    if (input.shape[0] > kPromptMinRows && fast_layout && (K / 8) % 4 == 0 &&
+        prompt_gemm_eligible(true, weight->group_size, N, K, input.data, K, output.data, N)) {
+      GemmParams p{};
+      p.x = static_cast<const bf16*>(input.data); p.x_stride = K; p.M = int(input.shape[0]); p.K = K; p.N = N;
+      p.qweight = weight->qweight;
+      p.scales = static_cast<const bf16*>(weight->scales);
+      p.zeros = weight->zeros;
+      p.padded_groups = weight->padded_groups;
+      p.zero_stride = (K / 128 + 7) / 8;
+      p.bias = static_cast<const bf16*>(weight->bias);
+      p.out = static_cast<bf16*>(output.data); p.out_stride = N;
+      launch_prompt_gemm(true, p, stream, false);
+      return;
+    }
     for_row_groups(input.shape[0], [&](size_t first, size_t rows) {
       const bf16* x = static_cast<const bf16*>(input.data) + first * K;
       bf16* out = static_cast<bf16*>(output.data) + first * N;

@@ -1,0 +1,62 @@
+// Host side of the prompt GEMM: eligibility, tensor maps, launch.
+#include "prompt_gemm.cuh"
+
+#include <stdexcept>
+
+namespace ei {
+
+namespace {
+bool aligned_16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace
+
+bool prompt_gemm_eligible(bool awq, int group_size, int N, int K, const void* x, int x_stride, const void* out,
+                          int out_stride) {
+  if (N < 16 || N % 16 || K < kPromptBlockK || K % kPromptBlockK) return false;
+  if (awq && (group_size != 128 || K % 128)) return false;
+  return aligned_16(x) && x_stride % 8 == 0 && aligned_16(out) && out_stride % 8 == 0;
+}
+
+void launch_prompt_gemm(bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
+  if (p.M < 1) throw std::invalid_argument("prompt GEMM needs at least one row");
+  PromptMaps maps{};
+  {
+    const cuuint64_t dims[2] = {cuuint64_t(p.K), cuuint64_t(p.M)};
+    const cuuint64_t strides[1] = {cuuint64_t(p.x_stride) * 2};
+    const cuuint32_t box[2] = {kPromptBlockK, kPromptTokens};
+    encode_map(&maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+               "prompt activations");
+  }
+  if (awq) {
+    if (!aligned_16(p.qweight) || (p.K / 8) % 4) throw std::invalid_argument("prompt GEMM: packed weight rows must be 16-byte aligned");
+    const cuuint64_t dims[2] = {cuuint64_t(p.K / 8), cuuint64_t(p.N)};
+    const cuuint64_t strides[1] = {cuuint64_t(p.K / 8) * 4};
+    const cuuint32_t box[2] = {kPromptBlockK / 8, kPromptFeatures};
+    encode_map(&maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, p.qweight, dims, strides, box,
+               CU_TENSOR_MAP_SWIZZLE_NONE, "prompt int4 weights");
+  } else {
+    if (!aligned_16(p.w) || p.ldw % 8) throw std::invalid_argument("prompt GEMM: weight rows must be 16-byte aligned");
+    const cuuint64_t dims[2] = {cuuint64_t(p.K), cuuint64_t(p.N)};
+    const cuuint64_t strides[1] = {cuuint64_t(p.ldw) * 2};
+    const cuuint32_t box[2] = {kPromptBlockK, kPromptFeatures};
+    encode_map(&maps.weights, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w, dims, strides, box,
+               CU_TENSOR_MAP_SWIZZLE_128B, "prompt weights");
+  }
+  static thread_local int configured_device = -1;
+  int device = 0;
+  EI_CUDA(cudaGetDevice(&device));
+  if (configured_device != device) {
+    EI_CUDA(cudaFuncSetAttribute(prompt_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kPromptSharedBytes)));
+    EI_CUDA(cudaFuncSetAttribute(prompt_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kPromptSharedBytes)));
+    configured_device = device;
+  }
+  const dim3 grid((p.N + kPromptFeatures - 1) / kPromptFeatures,
+                  (p.M + kPromptTokens * kPromptTokenTiles - 1) / (kPromptTokens * kPromptTokenTiles));
+  if (awq)
+    launch(prompt_gemm_kernel<true>, grid, dim3(kPromptThreads), kPromptSharedBytes, stream, pdl, maps, p);
+  else
+    launch(prompt_gemm_kernel<false>, grid, dim3(kPromptThreads), kPromptSharedBytes, stream, pdl, maps, p);
+}
+
+}  // namespace ei

@@ -1,6 +1,7 @@
 // Dispatch, planning and fallbacks for the small-M weight-streaming GEMM.
 #include "awq_tma.cuh"
 #include "dense_tma.cuh"
+#include "prompt_gemm.cuh"
 
 #include <algorithm>
 #include <stdexcept>
@@ -145,6 +146,8 @@ EncodeTiled tensor_map_encoder() {
   return encoder;
 }
 
+}  // namespace
+
 void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
                 const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle, const char* what) {
   const cuuint32_t ones[3] = {1, 1, 1};
@@ -155,6 +158,8 @@ void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void
     throw std::runtime_error(std::string("Tensor map for ") + what + " could not be encoded: " +
                              std::to_string(int(result)));
 }
+
+namespace {
 
 bool aligned_16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

@@ -380,4 +380,15 @@ GemmPlan plan_gemm(bool awq, int M, int N, int K, int epilogue, int multiprocess
                    size_t smem_limit, bool allow_split);
 void launch_gemm(const GemmPlan& plan, bool awq, const GemmParams& params, cudaStream_t stream, bool pdl);
 
+// ---- prompt GEMM (prompt_gemm.cuh): many rows at once on tcgen05 ----
+constexpr int kPromptMinRows = 32;  // more rows than this take the prompt kernel where the shape allows
+// True if the prompt kernel takes this shape (features in steps of 16, inputs in steps of a K block - of a
+// quantisation group for int4 - and 16-byte aligned rows).
+bool prompt_gemm_eligible(bool awq, int group_size, int N, int K, const void* x, int x_stride, const void* out,
+                          int out_stride);
+// out[T, N] = x[T, K] * W^T (+ bias), rounded once to BF16. Uses p.x, x_stride, M (= T), K, N, the weight
+// fields of its kind, bias, out, out_stride, status, wait_limit, fault_tx.
+void launch_prompt_gemm(bool awq, const GemmParams& p, cudaStream_t stream, bool pdl);
+
+
 }  // namespace ei
