@@ -60,24 +60,33 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                : "r"(address));
 }
 
+// kDirect = false: the verify step. Block (split, kv head) covers one chunk of the sequence for all <= 16 query
+// rows and writes (o, m, l) partials for the merge kernel.
+// kDirect = true: a prompt of many rows. Block (query block, kv head) covers 16 consecutive query rows over their
+// whole causal history and writes the normalised output itself; blocks with the longest histories start first.
+template <bool kDirect>
 __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   // The context length was written by the previous step; the preceding kernel of this step only appends the
   // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
-  const int offset = p.device_offset ? *p.device_offset : p.host_offset;
-  const int length = offset + p.rows;
-  const int split = blockIdx.x, kv_head = blockIdx.y;
-  const int start = split * p.chunk;
-  if (offset < 0 || length > p.capacity) {
+  const int first_offset = p.device_offset ? *p.device_offset : p.host_offset;
+  const int kv_head = blockIdx.y;
+  if (first_offset < 0 || first_offset + p.rows > p.capacity) {
     // The whole grid leaves: it still waits for its predecessor first, so that a successor never sees this
     // kernel complete before the kernels ahead of it have.
     grid_dependency_wait();
     return;
   }
+  const int first_row = kDirect ? (int(gridDim.x) - 1 - int(blockIdx.x)) * 16 : 0;
+  const int rows = kDirect ? min(16, p.rows - first_row) : p.rows;
+  const int offset = first_offset + first_row;
+  const int length = offset + rows;
+  const int split = kDirect ? 0 : blockIdx.x;
+  const int start = kDirect ? 0 : split * p.chunk;
   if (start >= length) return;  // other blocks of the grid wait
-  const int end = min(start + p.chunk, length);
+  const int end = kDirect ? length : min(start + p.chunk, length);
   const int group = p.heads / p.kv_heads;
-  const int stacked = p.rows * group;  // query rows served by this block
+  const int stacked = rows * group;  // query rows served by this block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
 
   unsigned char* k_smem[2] = {smem, smem + 2 * kTileBytes};
@@ -102,8 +111,8 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   const int h_hi = kv_head * group + (live_hi ? i_hi % group : 0);
   uint32_t qa[8][4];
   {
-    const bf16* q_lo = p.q + size_t(r_lo) * p.q_stride + size_t(h_lo) * kDim;
-    const bf16* q_hi = p.q + size_t(r_hi) * p.q_stride + size_t(h_hi) * kDim;
+    const bf16* q_lo = p.q + size_t(first_row + r_lo) * p.q_stride + size_t(h_lo) * kDim;
+    const bf16* q_hi = p.q + size_t(first_row + r_hi) * p.q_stride + size_t(h_hi) * kDim;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
       qa[kk][0] = live_lo ? *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 2 * c) : 0u;
@@ -214,6 +223,22 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 
+  if (kDirect) {
+    const float inverse_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, inverse_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
+    if (live_lo) {
+      bf16* dst = p.out + size_t(first_row + r_lo) * p.out_stride + size_t(h_lo) * kDim;
+#pragma unroll
+      for (int d = 0; d < 16; ++d)
+        *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * c) = pack_bf16(o[d][0] * inverse_lo, o[d][1] * inverse_lo);
+    }
+    if (live_hi) {
+      bf16* dst = p.out + size_t(first_row + r_hi) * p.out_stride + size_t(h_hi) * kDim;
+#pragma unroll
+      for (int d = 0; d < 16; ++d)
+        *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * c) = pack_bf16(o[d][2] * inverse_hi, o[d][3] * inverse_hi);
+    }
+    return;
+  }
   const size_t slots = size_t(p.rows) * p.heads;
   if (live_lo) {
     float* dst = p.scratch + (size_t(split) * slots + size_t(r_lo) * p.heads + h_lo) * kPartial;
@@ -320,20 +345,34 @@ size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length) {
   return splits * rows * heads * kPartial * sizeof(float);
 }
 
-void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
-  const int group = p.heads / p.kv_heads;
-  const int warps = (p.rows * group + 15) / 16;
+namespace {
+void configure_attention_kernels() {
   static thread_local int configured_device = -1;
   int device = 0;
   EI_CUDA(cudaGetDevice(&device));
-  if (configured_device != device) {
-    EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 4 * kTileBytes));
-    configured_device = device;
-  }
-  launch(verify_attention_kernel, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
+  if (configured_device == device) return;
+  EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               4 * kTileBytes));
+  EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               4 * kTileBytes));
+  configured_device = device;
+}
+}  // namespace
+
+void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+  const int group = p.heads / p.kv_heads;
+  const int warps = (p.rows * group + 15) / 16;
+  configure_attention_kernels();
+  launch(verify_attention_kernel<false>, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
          stream, pdl, p);
   launch(attention_merge_kernel, dim3(p.rows * p.heads), dim3(128), 0, stream, pdl, p);
+}
+
+void launch_prompt_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+  const int group = p.heads / p.kv_heads;
+  configure_attention_kernels();
+  launch(verify_attention_kernel<true>, dim3((p.rows + 15) / 16, p.kv_heads), dim3(group * 32),
+         size_t(4 * kTileBytes), stream, pdl, p);
 }
 
 }  // namespace ei

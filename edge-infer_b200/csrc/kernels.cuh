@@ -108,6 +108,9 @@ struct AttentionParams {
 int attention_chunk_for(size_t kv_length);
 size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length);
 void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);
+// Any number of query rows in one launch, 16 per block over their whole causal history; no scratch, no merge
+// (chunk, max_splits and scratch are not used).
+void launch_prompt_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);
 
 // ---- sampling.cu ----
 // Per-row argmax partials of logits [rows, vocab] into best_value / best_index [blocks, 16]; at most

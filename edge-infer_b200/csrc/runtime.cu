@@ -13,6 +13,7 @@
 #include <limits>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -104,6 +105,18 @@ struct ei_model {
   size_t weight_bytes = 0;
   int multiprocessors = 1;  // queried at creation
   size_t smem_limit = 227 * 1024;
+  // Activations of a prompt segment (up to kPromptSegment rows through every projection at once): one set per
+  // model, created by the first long prompt and lent, under the mutex, to one prefill at a time.
+  struct PromptWorkspace {
+    std::mutex mutex;
+    unsigned char* arena = nullptr;
+    size_t rows = 0;
+    bf16 *residual = nullptr, *normed = nullptr, *qkv = nullptr, *attention = nullptr, *gate_up = nullptr,
+         *act = nullptr, *projection = nullptr;
+    uint32_t *tokens = nullptr, *step_tokens = nullptr;
+    uint32_t* host_tokens = nullptr;  // pinned
+  } prompt;
+  bool prompt_ready = false;  // every projection of every layer has a shape the prompt GEMM takes
 };
 
 namespace {
@@ -280,6 +293,7 @@ struct ei_session {
   uint32_t inject_wait_polls = 0;  // test hook: the next weight-streaming GEMM gets this poll limit and a copy
                                    // expectation it cannot meet, so that its bounded waits run out
   size_t launches = 0, launches_per_step[kMaxRows + 1] = {};
+  size_t prefill_target_row = 0;  // where in `targets` the last prefill left the greedy token of its last row
   // graphs: [kind][rows]; kind 0 verify (host tokens), 1 verify (device drafts), 2 decode (commit all)
   cudaGraphExec_t graphs[3][kMaxRows + 1] = {};
 };
@@ -442,6 +456,178 @@ void run_projection_residual_norm(ei_session& s, const PreparedLinear& w, const 
     launch(residual_norm_bf16_kernel, dim3(rows), dim3(512), 0, s.stream, pdl, (const bf16*)s.projection,
            int(c.hidden_size), s.residual, norm_weight, c.rms_norm_eps, s.normed);
   }
+}
+
+constexpr size_t kPromptSegment = 2048;  // rows of a long prompt that go through the layers together
+
+bool prompt_linear_ok(const PreparedLinear& w) {
+  if (w.quantized && (w.in / 8) % 4) return false;
+  const void* weights = w.quantized ? static_cast<const void*>(w.qweight) : static_cast<const void*>(w.dense);
+  return (reinterpret_cast<uintptr_t>(weights) & 15) == 0 &&
+         prompt_gemm_eligible(w.quantized, w.group_size, w.out, w.in, nullptr, w.in, nullptr, w.out);
+}
+
+void ensure_prompt_workspace(ei_model& m) {
+  auto& ws = m.prompt;
+  if (ws.arena) return;
+  const auto& c = m.config;
+  const size_t rows = std::min<size_t>(kPromptSegment, c.max_position_embeddings);
+  const size_t H = c.hidden_size, F = c.intermediate_size, Q = c.n_heads * 128;
+  const size_t qkv_width = (c.n_heads + 2 * c.n_kv_heads) * 128;
+  size_t offset = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = offset;
+    offset += aligned(bytes);
+    return at;
+  };
+  const size_t o_residual = take(rows * H * 2), o_normed = take(rows * H * 2), o_qkv = take(rows * qkv_width * 2);
+  const size_t o_attention = take(rows * Q * 2), o_gate_up = take(rows * 2 * F * 2), o_act = take(rows * F * 2);
+  const size_t o_projection = take(rows * H * 2), o_tokens = take(rows * 4), o_step = take(rows * 4);
+  unsigned char* base = nullptr;
+  EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&base), offset));
+  if (cudaMallocHost(reinterpret_cast<void**>(&ws.host_tokens), rows * 4) != cudaSuccess) {
+    cudaFree(base);
+    throw std::runtime_error("Prompt staging buffer could not be allocated");
+  }
+  ws.residual = reinterpret_cast<bf16*>(base + o_residual);
+  ws.normed = reinterpret_cast<bf16*>(base + o_normed);
+  ws.qkv = reinterpret_cast<bf16*>(base + o_qkv);
+  ws.attention = reinterpret_cast<bf16*>(base + o_attention);
+  ws.gate_up = reinterpret_cast<bf16*>(base + o_gate_up);
+  ws.act = reinterpret_cast<bf16*>(base + o_act);
+  ws.projection = reinterpret_cast<bf16*>(base + o_projection);
+  ws.tokens = reinterpret_cast<uint32_t*>(base + o_tokens);
+  ws.step_tokens = reinterpret_cast<uint32_t*>(base + o_step);
+  ws.rows = rows;
+  ws.arena = base;
+}
+
+void run_prompt_linear(ei_session& s, const PreparedLinear& w, const bf16* x, int rows, bf16* out, bool pdl) {
+  GemmParams p{};
+  p.x = x;
+  p.x_stride = w.in;
+  p.M = rows;
+  p.K = w.in;
+  p.N = w.out;
+  p.qweight = w.qweight;
+  p.scales = w.scales;
+  p.zeros = w.zeros;
+  p.padded_groups = w.padded_groups;
+  p.zero_stride = w.zero_stride;
+  p.w = w.dense;
+  p.ldw = w.in;
+  p.bias = w.bias;
+  p.out = out;
+  p.out_stride = w.out;
+  p.status = &s.control->status;
+  if (s.inject_wait_polls) {
+    p.wait_limit = s.inject_wait_polls;
+    p.fault_tx = 16;
+    s.inject_wait_polls = 0;  // one launch only
+  }
+  tick(s);
+  launch_prompt_gemm(w.quantized, p, s.stream, pdl);
+}
+
+// One forward of `rows` prompt tokens (any number up to the workspace's) at the device-side context length:
+// every projection is one tcgen05 GEMM over all rows, attention one launch over all rows. All rows are
+// committed; with `head`, the last row alone goes through the vocabulary head (logits in s.logits, its greedy
+// token in s.targets[0]).
+void enqueue_prompt_segment(ei_session& s, int rows, bool head) {
+  ei_model& m = *s.model;
+  auto& ws = m.prompt;
+  const auto& c = m.config;
+  const int heads = int(c.n_heads), kv_heads = int(c.n_kv_heads), hidden = int(c.hidden_size), ffn = int(c.intermediate_size);
+  const int qkv_width = (heads + 2 * kv_heads) * 128, kv_width = kv_heads * 128;
+  const bool pdl = true;
+
+  EmbedParams e{};
+  e.tokens = ws.tokens;
+  e.control = s.control;
+  e.step_tokens = ws.step_tokens;
+  e.table = m.embedding;
+  e.vocab = int(c.vocab_size);
+  e.hidden = hidden;
+  e.rows = rows;
+  e.capacity = int(s.capacity);
+  e.norm_weight = m.layers[0].attention_norm;
+  e.eps = c.rms_norm_eps;
+  e.residual = ws.residual;
+  e.normed = ws.normed;
+  tick(s);
+  launch_embed_norm(e, s.stream, false);
+
+  const int elementwise_blocks = m.multiprocessors * 8;
+  for (size_t layer = 0; layer < m.layers.size(); ++layer) {
+    const auto& L = m.layers[layer];
+    run_prompt_linear(s, L.qkv, ws.normed, rows, ws.qkv, pdl);
+    QkvParams q{};
+    q.qkv = ws.qkv;
+    q.rows = rows;
+    q.heads = heads;
+    q.kv_heads = kv_heads;
+    q.qkv_stride = qkv_width;
+    q.q_norm = c.qk_norm ? L.q_norm : nullptr;
+    q.k_norm = c.qk_norm ? L.k_norm : nullptr;
+    q.eps = c.rms_norm_eps;
+    q.rope_table = m.rope_table;
+    q.max_positions = int(c.max_position_embeddings);
+    q.control = s.control;
+    q.capacity = int(s.capacity);
+    q.k_cache = s.k_cache + layer * s.capacity * kv_width;
+    q.v_cache = s.v_cache + layer * s.capacity * kv_width;
+    tick(s);
+    launch_qk_norm_rope_store(q, s.stream, pdl);
+
+    AttentionParams a{};
+    a.q = ws.qkv;
+    a.q_stride = qkv_width;
+    a.k = q.k_cache;
+    a.v = q.v_cache;
+    a.kv_stride = kv_width;
+    a.rows = rows;
+    a.heads = heads;
+    a.kv_heads = kv_heads;
+    a.capacity = int(s.capacity);
+    a.device_offset = &s.control->context;
+    a.out = ws.attention;
+    a.out_stride = heads * 128;
+    tick(s);
+    launch_prompt_attention(a, s.stream, pdl);
+
+    run_prompt_linear(s, L.o, ws.attention, rows, ws.projection, pdl);
+    tick(s);
+    launch(residual_norm_bf16_kernel, dim3(rows), dim3(512), 0, s.stream, pdl, (const bf16*)ws.projection, hidden,
+           ws.residual, L.ffn_norm, c.rms_norm_eps, ws.normed);
+
+    run_prompt_linear(s, L.gate_up, ws.normed, rows, ws.gate_up, pdl);
+    tick(s);
+    launch(silu_pair_rows_kernel, dim3(elementwise_blocks), dim3(256), 0, s.stream, pdl, (const bf16*)ws.gate_up, rows,
+           ffn, ws.act);
+    const bf16* next_norm = layer + 1 < m.layers.size() ? m.layers[layer + 1].attention_norm : m.output_norm;
+    run_prompt_linear(s, L.down, ws.act, rows, ws.projection, pdl);
+    tick(s);
+    launch(residual_norm_bf16_kernel, dim3(rows), dim3(512), 0, s.stream, pdl, (const bf16*)ws.projection, hidden,
+           ws.residual, next_norm, c.rms_norm_eps, ws.normed);
+  }
+
+  if (head) {
+    const bf16* last = ws.normed + size_t(rows - 1) * hidden;
+    int parts = 0;
+    if (has_plan(s, m.lm_head, 1, kEpiArgmax)) {
+      run_linear(s, m.lm_head, last, 1, kEpiArgmax, s.logits, int(c.vocab_size), pdl, &parts);
+    } else {
+      run_generic(s, m.lm_head, last, 1, s.logits, pdl);
+      parts = std::min(kSampleMaxParts, sample_partial_blocks(c.vocab_size, m.multiprocessors));
+      tick(s);
+      launch_argmax_partials(s.logits, 1, c.vocab_size, c.vocab_size, s.best_value, s.best_index, parts, s.stream, pdl);
+    }
+    tick(s);
+    launch_finalize(s.best_value, s.best_index, parts, 1, s.targets, nullptr, nullptr, nullptr, nullptr, nullptr,
+                    s.stream, pdl);
+  }
+  tick(s);
+  launch(commit_rows_kernel, dim3(1), dim3(32), 0, s.stream, pdl, s.control, rows);
 }
 
 // Enqueues one forward of `rows` tokens at the device-side context length.
@@ -834,6 +1020,10 @@ ei_status ei_model_create(const ei_model_config* config, const ei_named_tensor* 
       if (ei_build_rope_table(table.data(), c.max_position_embeddings, c.head_dim, c.rope_theta) != EI_OK)
         throw std::invalid_argument(g_last_error);
       model->rope_table = static_cast<float*>(builder.place(table.data(), rope_bytes));
+      model->prompt_ready = true;
+      for (const auto& L : model->layers)
+        model->prompt_ready = model->prompt_ready && prompt_linear_ok(L.qkv) && prompt_linear_ok(L.o) &&
+                              prompt_linear_ok(L.gate_up) && prompt_linear_ok(L.down);
       EI_CUDA(cudaDeviceSynchronize());
     } catch (...) {
       cudaFree(model->arena);
@@ -849,6 +1039,8 @@ void ei_model_destroy(ei_model* model) {
   cudaGetDevice(&previous);
   if (previous != model->device) cudaSetDevice(model->device);
   cudaFree(model->arena);
+  if (model->prompt.arena) cudaFree(model->prompt.arena);
+  if (model->prompt.host_tokens) cudaFreeHost(model->prompt.host_tokens);
   if (previous != model->device) cudaSetDevice(previous);
   delete model;
 }
@@ -970,13 +1162,30 @@ ei_status ei_session_prefill(ei_session* session, const uint32_t* host_tokens, s
     const size_t vocab = s.model->config.vocab_size;
     for (size_t i = 0; i < rows; ++i)
       if (host_tokens[i] >= vocab) throw std::invalid_argument("Token exceeds vocabulary");
+    // Long prompts go through the layers in segments of up to kPromptSegment rows, on the model's prompt
+    // workspace, which this call holds until its stream has drained.
+    const bool wide = rows > size_t(kPromptMinRows) && !all_logits && s.model->prompt_ready;
+    std::unique_lock<std::mutex> workspace(s.model->prompt.mutex, std::defer_lock);
+    if (wide) workspace.lock();
     try {
       // A prefill replaces the history (the reference resizes the managed cache to `rows`).
       EI_CUDA(cudaMemsetAsync(s.control, 0, sizeof(Control), s.stream));
       s.context = 0;
       s.bound = 0;
       s.history_ready = false;
-      for (size_t first = 0; first < rows; first += kMaxRows) {
+      s.prefill_target_row = wide ? 0 : (rows - 1) % kMaxRows;
+      if (wide) {
+        ensure_prompt_workspace(*s.model);
+        auto& ws = s.model->prompt;
+        for (size_t first = 0; first < rows; first += ws.rows) {
+          const size_t count = std::min(ws.rows, rows - first);
+          synchronize(s);  // the pinned staging buffer is reused by every segment
+          std::memcpy(ws.host_tokens, host_tokens + first, count * 4);
+          EI_CUDA(cudaMemcpyAsync(ws.tokens, ws.host_tokens, count * 4, cudaMemcpyHostToDevice, s.stream));
+          enqueue_prompt_segment(s, int(count), first + count >= rows);
+        }
+      }
+      for (size_t first = wide ? rows : 0; first < rows; first += kMaxRows) {
         const int chunk = int(std::min<size_t>(kMaxRows, rows - first));
         const bool last = first + chunk >= rows;
         synchronize(s);  // the pinned staging buffer is reused by every chunk
@@ -1394,7 +1603,7 @@ ei_status ei_speculative_prefill(ei_speculative* spec, const uint32_t* host_toke
       if (ei_session_prefill(s, host_tokens, rows, nullptr, nullptr) != EI_OK)
         throw std::runtime_error("Speculative prefill failed: " + g_last_error);
     try {
-      const size_t last_row = (rows - 1) % kMaxRows;
+      const size_t last_row = t.prefill_target_row;
       uint32_t first = 0;
       EI_CUDA(cudaMemcpyAsync(t.host_tokens, t.targets + last_row, sizeof(uint32_t), cudaMemcpyDeviceToHost, t.stream));
       synchronize(t);
