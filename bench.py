@@ -332,6 +332,10 @@ def time_reference_cuda(package, oracle, torch, shape, tensors, drafts, first, s
     del host
     prompt = package.synthetic.make_prompt(SEED, PROMPT, shape.vocab_size)
     reference.forward(prompt, want_logits=False)
+    reference.resize(0)
+    begin = time.perf_counter()
+    reference.forward(prompt, want_logits=False)   # the reference's own prompt prefill, warm
+    prompt_seconds = time.perf_counter() - begin
 
     def run(count: int):
         emitted_total, offset, pending = 0, 0, first
@@ -355,7 +359,27 @@ def time_reference_cuda(package, oracle, torch, shape, tensors, drafts, first, s
     seconds, emitted = run(steps)
     del reference
     torch.cuda.empty_cache()
-    return seconds / steps, emitted / steps
+    return seconds / steps, emitted / steps, prompt_seconds
+
+
+def prompt_leg(shape, ms: float) -> dict:
+    """Prefill of the benchmark's 2048-token prompt through the public call. The arithmetic counted is the four
+    projections of every layer over all rows (2 * rows * N * K each) and causal attention (QK and PV over half the
+    square); the denominator is the measured sustained BF16 GEMM rate."""
+    rows, hidden, ffn = PROMPT, shape.hidden_size, shape.intermediate_size
+    qkv = (shape.n_heads + 2 * shape.n_kv_heads) * shape.head_dim
+    per_layer = 2.0 * rows * hidden * (qkv + shape.n_heads * shape.head_dim + 3 * ffn)
+    attention = 2.0 * 2.0 * shape.n_heads * shape.head_dim * rows * rows / 2.0
+    flops = shape.n_layers * (per_layer + attention)
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    achieved = flops / (ms * 1e-3) / 1e12
+    return {"rows": rows, "ms": ms, "value": rows / (ms * 1e-3), "unit": "prompt tokens/s",
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak,
+                         "peak_source": "measured (sustained)" if peaks else "fallback"},
+            "what": "session prefill of the 2048-token prompt, host tokens in, median of 3 calls; projections on "
+                    "tcgen05 (int4 dequantised in shared memory), one attention launch over all rows"}
 
 
 def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int):
@@ -478,6 +502,14 @@ def run_native(args, rank: int, world: int, local_rank: int):
     session = model.new_session(CAPACITY, graph=True)
     prompt = syn.make_prompt(SEED, PROMPT, shape.vocab_size)
     session.prefill(prompt)
+    # The prompt leg: the same prefill again, timed on the host around the public call (host tokens in, one
+    # synchronisation at its end).
+    prompt_ms = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        session.prefill(prompt)
+        prompt_ms.append((time.perf_counter() - begin) * 1e3)
     first = package.runtime.greedy_token(session.read_logits(1)[0])
 
     # The model's own greedy continuation (ordinary decoding), then corrupted drafts.
@@ -610,6 +642,7 @@ def run_native(args, rank: int, world: int, local_rank: int):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": 96,
                     "ms_per_step": times[regions] / args.steps},
             "gpu_launches": int(launches * args.steps),
+            "prompt_leg": prompt_leg(shape, sorted(prompt_ms)[1]),
             "step_roofline": {"bound": "hbm", "achieved": step_achieved, "peak": peak, "unit": "GB/s",
                               "frac": step_achieved / peak, "peak_source": peak_kind, "bytes_per_step": step_bytes,
                               "launches_per_step": int(launches)},
@@ -630,13 +663,15 @@ def run_native(args, rank: int, world: int, local_rank: int):
             oracle = entry.load_oracle()
             if oracle.reference_available():
                 try:
-                    step_seconds, tokens = time_reference_cuda(package, oracle, torch, shape, keep_tensors, drafts, first,
+                    step_seconds, tokens, reference_prompt_seconds = time_reference_cuda(package, oracle, torch, shape, keep_tensors, drafts, first,
                                                                max(10, min(args.steps, 40)))
                     same_drafts = line["config"]["tokens_per_step"]
                     line["reference_cuda"] = {
                         "ms_per_step": step_seconds * 1e3, "value": same_drafts / step_seconds, "unit": UNIT,
                         "speedup_e2e_ms_per_step": step_seconds * 1e3 / line["e2e"]["ms_per_step"],
                         "tokens_per_step_observed": tokens,
+                        "prompt_ms": reference_prompt_seconds * 1e3,
+                        "prompt_speedup": reference_prompt_seconds * 1e3 / line["prompt_leg"]["ms"],
                         "what": "unmodified reference (oracle/_ref, its kernels recompiled for sm_100): "
                                 "prefill_eager of 9 rows + op::cuda::sample + host acceptance, same model, GPU and "
                                 "step shape; `value` uses this bench's accept lengths (the step time does not depend "

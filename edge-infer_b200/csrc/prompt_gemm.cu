@@ -1,6 +1,7 @@
 // Host side of the prompt GEMM: eligibility, tensor maps, launch.
 #include "prompt_gemm.cuh"
 
+#include <algorithm>
 #include <stdexcept>
 
 namespace ei {
@@ -14,6 +15,19 @@ bool prompt_gemm_eligible(bool awq, int group_size, int N, int K, const void* x,
   if (N < 16 || N % 16 || K < kPromptBlockK || K % kPromptBlockK) return false;
   if (awq && (group_size != 128 || K % 128)) return false;
   return aligned_16(x) && x_stride % 8 == 0 && aligned_16(out) && out_stride % 8 == 0;
+}
+
+// Slices of K that bring the grid to about one block per SM, each slice at least 8 K blocks long, within the
+// room of the partial buffer.
+int prompt_gemm_ksplit(int rows, int N, int K, int multiprocessors, size_t partial_bytes) {
+  const int blocks = ((N + kPromptFeatures - 1) / kPromptFeatures) *
+                     ((rows + kPromptTokens * kPromptTokenTiles - 1) / (kPromptTokens * kPromptTokenTiles));
+  int ksplit = std::max(1, multiprocessors / std::max(1, blocks));
+  ksplit = std::min(ksplit, std::max(1, K / (8 * kPromptBlockK)));
+  ksplit = std::min(ksplit, 16);
+  if (K % 128) ksplit = 1;
+  while (ksplit > 1 && size_t(ksplit) * rows * N * sizeof(float) > partial_bytes) --ksplit;
+  return ksplit;
 }
 
 void launch_prompt_gemm(bool awq, const GemmParams& p, cudaStream_t stream, bool pdl) {
@@ -51,12 +65,20 @@ void launch_prompt_gemm(bool awq, const GemmParams& p, cudaStream_t stream, bool
                                  int(kPromptSharedBytes)));
     configured_device = device;
   }
+  const int ksplit = p.epilogue == kEpiPartial ? std::max(1, p.ksplit) : 1;
+  if (p.epilogue != kEpiStore && p.epilogue != kEpiPartial)
+    throw std::invalid_argument("prompt GEMM stores BF16 outputs or FP32 partial sums");
+  if (ksplit > 1 && (p.K % 128 || ksplit > p.K / 128)) throw std::invalid_argument("prompt GEMM: K split too fine");
+  if (p.epilogue == kEpiPartial && (!p.partial || (reinterpret_cast<uintptr_t>(p.partial) & 15) || p.N % 4))
+    throw std::invalid_argument("prompt GEMM: partial sums need a 16-byte aligned buffer");
+  GemmParams q = p;
+  q.ksplit = ksplit;
   const dim3 grid((p.N + kPromptFeatures - 1) / kPromptFeatures,
-                  (p.M + kPromptTokens * kPromptTokenTiles - 1) / (kPromptTokens * kPromptTokenTiles));
+                  (p.M + kPromptTokens * kPromptTokenTiles - 1) / (kPromptTokens * kPromptTokenTiles), ksplit);
   if (awq)
-    launch(prompt_gemm_kernel<true>, grid, dim3(kPromptThreads), kPromptSharedBytes, stream, pdl, maps, p);
+    launch(prompt_gemm_kernel<true>, grid, dim3(kPromptThreads), kPromptSharedBytes, stream, pdl, maps, q);
   else
-    launch(prompt_gemm_kernel<false>, grid, dim3(kPromptThreads), kPromptSharedBytes, stream, pdl, maps, p);
+    launch(prompt_gemm_kernel<false>, grid, dim3(kPromptThreads), kPromptSharedBytes, stream, pdl, maps, q);
 }
 
 }  // namespace ei

@@ -18,7 +18,9 @@
 //     accumulate in tensor memory - 2 token tiles x 256 FP32 columns = all 512 columns - and commits the stage's
 //     `empty` barrier, which hands the stage back to the copy thread;
 //   * after the last K block warps 0-7 read the accumulators with tcgen05.ld (warp w: lanes 32 (w % 4) ..., token
-//     tile w / 4), add the bias in FP32, round once to BF16 and store.
+//     tile w / 4), add the bias in FP32, round once to BF16 and store - or, for a projection whose sum the
+//     residual + norm kernel finishes, store FP32 partial sums, K split over blockIdx.z so that few token tiles
+//     still fill the SMs.
 // Rows beyond T and features beyond N are zero-filled by TMA and masked in the epilogue.
 //
 // Every wait on an mbarrier is bounded. A role whose wait runs out raises a flag in shared memory that every
@@ -130,7 +132,12 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kPromptFeatures, t0 = blockIdx.y * (kPromptTokens * kPromptTokenTiles);
   const int token_tiles = min(kPromptTokenTiles, (p.M - t0 + kPromptTokens - 1) / kPromptTokens);
-  const int k_blocks = p.K / kPromptBlockK;
+  // K slice of this block (blockIdx.z of p.ksplit): whole quantisation groups, i.e. pairs of K blocks.
+  const int slice = blockIdx.z;
+  const int pairs_total = p.K / (2 * kPromptBlockK);
+  const int kb_begin = p.ksplit > 1 ? int((long long)slice * pairs_total / p.ksplit) * 2 : 0;
+  const int kb_end = p.ksplit > 1 ? int((long long)(slice + 1) * pairs_total / p.ksplit) * 2 : p.K / kPromptBlockK;
+  const int k_blocks = kb_end - kb_begin;
   const uint32_t limit = p.wait_limit ? p.wait_limit : kAwqWaitLimit;
 
   if (threadIdx.x == 0) {
@@ -166,11 +173,12 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
         mbarrier_expect_tx(&sh->full[s], bytes + (kb == 0 ? p.fault_tx : 0u));
         unsigned char* base = stage_base(s);
         for (int mt = 0; mt < token_tiles; ++mt)
-          tma_load_2d(base + mt * kPromptTileBytes, &maps.x, kb * kPromptBlockK, t0 + mt * kPromptTokens, &sh->full[s]);
+          tma_load_2d(base + mt * kPromptTileBytes, &maps.x, (kb_begin + kb) * kPromptBlockK, t0 + mt * kPromptTokens,
+                      &sh->full[s]);
         if (kAwq)
-          tma_load_2d(base + kRawOffset, &maps.weights, kb * (kPromptBlockK / 8), n0, &sh->full[s]);
+          tma_load_2d(base + kRawOffset, &maps.weights, (kb_begin + kb) * (kPromptBlockK / 8), n0, &sh->full[s]);
         else
-          tma_load_2d(base + kWeightOffset, &maps.weights, kb * kPromptBlockK, n0, &sh->full[s]);
+          tma_load_2d(base + kWeightOffset, &maps.weights, (kb_begin + kb) * kPromptBlockK, n0, &sh->full[s]);
         issued = kb + 1;
       }
       if (sh->abort) {
@@ -222,25 +230,25 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
       for (int i = 0; i < 2; ++i) live_rows[i] = min(n0 + rows[i], p.N - 1);
       // Scales and zero points of a group are requested one group (two K blocks) before they are used.
       uint32_t scale2[2] = {0, 0}, zero_word[2] = {0, 0}, scale_next[2], zero_next[2];
-      const int groups = k_blocks >> 1;
+      const int group_begin = kb_begin >> 1, group_end = kb_end >> 1;
       auto request = [&](int g) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           scale_next[i] = uint32_t(__bfloat16_as_ushort(p.scales[size_t(live_rows[i]) * p.padded_groups + g])) * 0x10001u;
-          zero_next[i] = (g & 7) == 0 ? uint32_t(p.zeros[size_t(live_rows[i]) * p.zero_stride + (g >> 3)]) : zero_word[i];
+          zero_next[i] = ((g & 7) == 0 || g == group_begin) ? uint32_t(p.zeros[size_t(live_rows[i]) * p.zero_stride + (g >> 3)]) : zero_word[i];
         }
       };
-      request(0);
+      request(group_begin);
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % kPromptStages;
-        const int grp = kb >> 1;  // 128 inputs per group, 64 per K block
+        const int grp = (kb_begin + kb) >> 1;  // 128 inputs per group, 64 per K block
         if ((kb & 1) == 0) {
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             scale2[i] = scale_next[i];
             zero_word[i] = zero_next[i];
           }
-          if (grp + 1 < groups) request(grp + 1);
+          if (grp + 1 < group_end) request(grp + 1);
         }
         // The loop is left by whole warps: the barrier and the vote below are warp-wide.
         const bool arrived = prompt_wait(sh, &sh->full[s], (kb / kPromptStages) & 1, limit);
@@ -285,7 +293,12 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
         if (n0 + cb * 16 >= p.N) break;  // block-uniform
         float v[16];
         tmem_load16(tmem + (uint32_t(quarter * 32) << 16) + mt * kPromptFeatures + cb * 16, v);
-        if (token < p.M) {
+        if (token < p.M && p.epilogue == kEpiPartial) {
+          float* dst = p.partial + (size_t(slice) * p.M + token) * p.N + n0 + cb * 16;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else if (token < p.M) {
           uint32_t packed[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {

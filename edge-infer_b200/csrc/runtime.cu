@@ -58,6 +58,25 @@ __global__ void silu_pair_rows_kernel(const bf16* gate_up, int rows, int ffn, bf
   }
 }
 
+// The same over eight features per thread (ffn a multiple of 8, 16-byte aligned rows): the prompt path's form.
+__global__ void silu_pair_rows_vec_kernel(const bf16* gate_up, int rows, int ffn, bf16* out) {
+  grid_dependency_wait();
+  const int per_row = ffn / 8;
+  const long long total = (long long)rows * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = int(i / per_row), n = int(i - (long long)row * per_row) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gate_up + size_t(row) * 2 * ffn + n);
+    const uint4 u = *reinterpret_cast<const uint4*>(gate_up + size_t(row) * 2 * ffn + ffn + n);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      packed[j] = pack_bf16(silu_multiply_value(bf16_lo(gw[j]), bf16_lo(uw[j])),
+                            silu_multiply_value(bf16_hi(gw[j]), bf16_hi(uw[j])));
+    *reinterpret_cast<uint4*>(out + size_t(row) * ffn + n) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
 // residual += projection (BF16, already rounded with bias), then RMSNorm: the unfused fallback of
 // launch_residual_norm for shapes the streaming GEMM does not take.
 __global__ void __launch_bounds__(512) residual_norm_bf16_kernel(const bf16* projection, int hidden, bf16* residual,
@@ -113,6 +132,8 @@ struct ei_model {
     size_t rows = 0;
     bf16 *residual = nullptr, *normed = nullptr, *qkv = nullptr, *attention = nullptr, *gate_up = nullptr,
          *act = nullptr, *projection = nullptr;
+    float* partial = nullptr;         // FP32 sums of the o / down projections: [K slices][rows][hidden]
+    size_t partial_bytes = 0;
     uint32_t *tokens = nullptr, *step_tokens = nullptr;
     uint32_t* host_tokens = nullptr;  // pinned
   } prompt;
@@ -483,6 +504,9 @@ void ensure_prompt_workspace(ei_model& m) {
   const size_t o_residual = take(rows * H * 2), o_normed = take(rows * H * 2), o_qkv = take(rows * qkv_width * 2);
   const size_t o_attention = take(rows * Q * 2), o_gate_up = take(rows * 2 * F * 2), o_act = take(rows * F * 2);
   const size_t o_projection = take(rows * H * 2), o_tokens = take(rows * 4), o_step = take(rows * 4);
+  // Room for the FP32 sums of a full segment, or for 16 K slices of a short one.
+  const size_t partial_bytes = std::max(rows, size_t(16) * std::min<size_t>(rows, 256)) * H * sizeof(float);
+  const size_t o_partial = take(partial_bytes);
   unsigned char* base = nullptr;
   EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&base), offset));
   if (cudaMallocHost(reinterpret_cast<void**>(&ws.host_tokens), rows * 4) != cudaSuccess) {
@@ -498,12 +522,19 @@ void ensure_prompt_workspace(ei_model& m) {
   ws.projection = reinterpret_cast<bf16*>(base + o_projection);
   ws.tokens = reinterpret_cast<uint32_t*>(base + o_tokens);
   ws.step_tokens = reinterpret_cast<uint32_t*>(base + o_step);
+  ws.partial = reinterpret_cast<float*>(base + o_partial);
+  ws.partial_bytes = partial_bytes;
   ws.rows = rows;
   ws.arena = base;
 }
 
-void run_prompt_linear(ei_session& s, const PreparedLinear& w, const bf16* x, int rows, bf16* out, bool pdl) {
+// ksplit == 0: BF16 output with bias; otherwise FP32 partial sums of `ksplit` K slices in the workspace.
+void run_prompt_linear(ei_session& s, const PreparedLinear& w, const bf16* x, int rows, bf16* out, bool pdl,
+                       int ksplit = 0) {
   GemmParams p{};
+  p.epilogue = ksplit ? kEpiPartial : kEpiStore;
+  p.ksplit = ksplit;
+  p.partial = s.model->prompt.partial;
   p.x = x;
   p.x_stride = w.in;
   p.M = rows;
@@ -527,6 +558,37 @@ void run_prompt_linear(ei_session& s, const PreparedLinear& w, const bf16* x, in
   }
   tick(s);
   launch_prompt_gemm(w.quantized, p, s.stream, pdl);
+}
+
+// projection -> residual add -> RMSNorm over all rows of a segment: the projection leaves FP32 sums (K split
+// over blocks when few token tiles would leave SMs idle) that the residual + norm kernel finishes, as in the
+// verify step.
+void run_prompt_projection_residual_norm(ei_session& s, const PreparedLinear& w, const bf16* x, int rows,
+                                         const bf16* norm_weight, bool pdl) {
+  ei_model& m = *s.model;
+  auto& ws = m.prompt;
+  const auto& c = m.config;
+  if (w.out % 4 == 0 && size_t(rows) * w.out * sizeof(float) <= ws.partial_bytes) {
+    const int ksplit = prompt_gemm_ksplit(rows, w.out, w.in, m.multiprocessors, ws.partial_bytes);
+    run_prompt_linear(s, w, x, rows, nullptr, pdl, ksplit);
+    ResidualNormParams p{};
+    p.partial = ws.partial;
+    p.ksplit = ksplit;
+    p.rows = rows;
+    p.hidden = int(c.hidden_size);
+    p.bias = w.bias;
+    p.residual = ws.residual;
+    p.norm_weight = norm_weight;
+    p.eps = c.rms_norm_eps;
+    p.normed = ws.normed;
+    tick(s);
+    launch_residual_norm(p, s.stream, pdl);
+  } else {
+    run_prompt_linear(s, w, x, rows, ws.projection, pdl);
+    tick(s);
+    launch(residual_norm_bf16_kernel, dim3(rows), dim3(512), 0, s.stream, pdl, (const bf16*)ws.projection,
+           int(c.hidden_size), ws.residual, norm_weight, c.rms_norm_eps, ws.normed);
+  }
 }
 
 // One forward of `rows` prompt tokens (any number up to the workspace's) at the device-side context length:
@@ -595,20 +657,18 @@ void enqueue_prompt_segment(ei_session& s, int rows, bool head) {
     tick(s);
     launch_prompt_attention(a, s.stream, pdl);
 
-    run_prompt_linear(s, L.o, ws.attention, rows, ws.projection, pdl);
-    tick(s);
-    launch(residual_norm_bf16_kernel, dim3(rows), dim3(512), 0, s.stream, pdl, (const bf16*)ws.projection, hidden,
-           ws.residual, L.ffn_norm, c.rms_norm_eps, ws.normed);
+    run_prompt_projection_residual_norm(s, L.o, ws.attention, rows, L.ffn_norm, pdl);
 
     run_prompt_linear(s, L.gate_up, ws.normed, rows, ws.gate_up, pdl);
     tick(s);
-    launch(silu_pair_rows_kernel, dim3(elementwise_blocks), dim3(256), 0, s.stream, pdl, (const bf16*)ws.gate_up, rows,
-           ffn, ws.act);
+    if (ffn % 8 == 0)
+      launch(silu_pair_rows_vec_kernel, dim3(elementwise_blocks), dim3(256), 0, s.stream, pdl, (const bf16*)ws.gate_up,
+             rows, ffn, ws.act);
+    else
+      launch(silu_pair_rows_kernel, dim3(elementwise_blocks), dim3(256), 0, s.stream, pdl, (const bf16*)ws.gate_up, rows,
+             ffn, ws.act);
     const bf16* next_norm = layer + 1 < m.layers.size() ? m.layers[layer + 1].attention_norm : m.output_norm;
-    run_prompt_linear(s, L.down, ws.act, rows, ws.projection, pdl);
-    tick(s);
-    launch(residual_norm_bf16_kernel, dim3(rows), dim3(512), 0, s.stream, pdl, (const bf16*)ws.projection, hidden,
-           ws.residual, next_norm, c.rms_norm_eps, ws.normed);
+    run_prompt_projection_residual_norm(s, L.down, ws.act, rows, next_norm, pdl);
   }
 
   if (head) {

@@ -386,8 +386,11 @@ constexpr int kPromptMinRows = 32;  // more rows than this take the prompt kerne
 // quantisation group for int4 - and 16-byte aligned rows).
 bool prompt_gemm_eligible(bool awq, int group_size, int N, int K, const void* x, int x_stride, const void* out,
                           int out_stride);
-// out[T, N] = x[T, K] * W^T (+ bias), rounded once to BF16. Uses p.x, x_stride, M (= T), K, N, the weight
-// fields of its kind, bias, out, out_stride, status, wait_limit, fault_tx.
+// epilogue kEpiStore: out[T, N] = x[T, K] * W^T (+ bias), rounded once to BF16. kEpiPartial: FP32 partial sums
+// partial[ksplit][T][N] without bias, K split over ksplit blocks (whole groups of 128 inputs each).
+// Uses p.x, x_stride, M (= T), K, N, the weight fields of its kind, bias, out, out_stride, epilogue, ksplit,
+// partial, status, wait_limit, fault_tx.
+int prompt_gemm_ksplit(int rows, int N, int K, int multiprocessors, size_t partial_bytes);
 void launch_prompt_gemm(bool awq, const GemmParams& p, cudaStream_t stream, bool pdl);
 
 
