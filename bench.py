@@ -510,6 +510,14 @@ def run_native(args, rank: int, world: int, local_rank: int):
         begin = time.perf_counter()
         session.prefill(prompt)
         prompt_ms.append((time.perf_counter() - begin) * 1e3)
+    if args.profile_prompt:
+        torch.cuda.profiler.start()                    # for `ncu --profile-from-start off`: one prompt prefill only
+        session.prefill(prompt)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        if rank == 0:
+            print(json.dumps({"profiled": "one prefill of the %d-token prompt" % PROMPT, "ms": sorted(prompt_ms)[1]}))
+        return
     first = package.runtime.greedy_token(session.read_logits(1)[0])
 
     # The model's own greedy continuation (ordinary decoding), then corrupted drafts.
@@ -720,6 +728,8 @@ def main():
     parser.add_argument("--profile-region", action="store_true",
                         help="bracket the timed steps with cudaProfilerStart/Stop (for a profiler started with "
                              "profiling off); the numbers of such a run are not bench values")
+    parser.add_argument("--profile-prompt", action="store_true",
+                        help="bracket one prefill of the prompt the same way and stop after it")
     args = parser.parse_args()
     if args.steps is None:
         args.steps = 5 if args.impl == "reference" else 60

@@ -3,6 +3,8 @@
   AWQ int4 linear   M in {1,2,4,8,9,16} x (N,K) in {(4096,4096),(1024,4096),(24576,4096),(4096,12288)}
   verify attention  q_len in {1,5,9}, 32 Q / 8 KV heads, head_dim 128, KV length in {512,2048,8192,32768}
   dense BF16 head   (151936, 4096)
+  prompt GEMM       the same AWQ shapes at T in {128, 512, 2048} rows (the tcgen05 kernel the linear operators
+                    take above 32 rows), reported in TFLOP/s against the measured BF16 GEMM rate
 
 Every case cycles over enough distinct operand sets to exceed L2 (126 MB), is replayed from a CUDA graph so
 that host launch cost is excluded, and is timed with CUDA events. Prints one line per case:
@@ -10,6 +12,7 @@ time per launch, algorithmic bytes, achieved GB/s and the fraction of the measur
 
     python opbench.py                       # full sweep
     python opbench.py --op awq --n 24576 --k 4096 --rows 9 --fused   # one case (for ncu)
+    python opbench.py --op prompt --n 4096 --k 4096 --rows 512 --copies 2 --iters 1
 """
 from __future__ import annotations
 
@@ -26,6 +29,11 @@ import __graft_entry__ as entry  # noqa: E402
 def hbm_peak() -> float:
     path = ROOT / "MEASURED_PEAKS.json"
     return float(json.loads(path.read_text())["hbm_gbs"]) if path.exists() else 6650.0
+
+
+def tensor_peak() -> float:
+    path = ROOT / "MEASURED_PEAKS.json"
+    return float(json.loads(path.read_text())["bf16_tflops"]) if path.exists() else 1590.0
 
 
 def graph_time(torch, stream, body, iters: int) -> float:
@@ -124,7 +132,7 @@ def main():
     import torch
 
     parser = argparse.ArgumentParser()
-    parser.add_argument("--op", default="all", choices=["all", "awq", "dense", "attention"])
+    parser.add_argument("--op", default="all", choices=["all", "awq", "dense", "attention", "prompt"])
     parser.add_argument("--n", type=int, default=24576)
     parser.add_argument("--k", type=int, default=4096)
     parser.add_argument("--rows", type=int, default=9)
@@ -146,6 +154,15 @@ def main():
         print(f"{name:44s} {us:9.2f} us  {nbytes / 1e6:9.2f} MB  {gbs:8.1f} GB/s  {gbs / peak:6.3f} of measured HBM peak",
               flush=True)
 
+    def report_prompt(n, k, rows, us):
+        tflops = 2.0 * rows * n * k / us / 1e6
+        print(f"{f'prompt awq N={n} K={k} T={rows}':44s} {us:9.2f} us  {2.0 * rows * n * k / 1e9:9.2f} GFLOP  "
+              f"{tflops:8.1f} TFLOP/s  {tflops / tensor_peak():6.3f} of measured BF16 GEMM peak (burst)", flush=True)
+
+    if args.op == "prompt":
+        us, _ = bench_awq(torch, package, stream, ctx, args.n, args.k, args.rows, False, args.iters, args.copies or None)
+        report_prompt(args.n, args.k, args.rows, us)
+        return
     if args.op == "awq":
         us, nbytes = bench_awq(torch, package, stream, ctx, args.n, args.k, args.rows, args.fused, args.iters,
                                args.copies or None)
@@ -169,6 +186,10 @@ def main():
     for rows in [1, 9, 16]:
         us, nbytes = bench_dense(torch, package, stream, ctx, 151936, 4096, rows, args.iters)
         report(f"dense N=151936 K=4096 M={rows}", us, nbytes)
+    for n, k in [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]:
+        for rows in [128, 512, 2048]:
+            us, _ = bench_awq(torch, package, stream, ctx, n, k, rows, False, args.iters)
+            report_prompt(n, k, rows, us)
     for length in [512, 2048, 8192, 32768]:
         for rows in [1, 5, 9]:
             us, nbytes = bench_attention(torch, package, stream, ctx, rows, length, args.iters)
