@@ -384,9 +384,12 @@ def prompt_leg(shape, ms: float) -> dict:
 
 def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int):
     """The sharded-sessions configuration: 64 sessions of the Qwen2.5-7B-shaped AWQ model with seeded prompt lengths
-    in [256, 8192], split evenly over the ranks, k = 4 drafts with p = 0.3 substitution, three sessions stacked per
-    forward. The histories are SYNTHETIC: every session's K/V rows are seeded with random BF16 values and adopted
-    (no prefill of 270 000 prompt tokens); the drafts are each session's own greedy continuation from there."""
+    in [256, 8192], split evenly over the ranks, k = 4 drafts with p = 0.3 substitution. Every forward verifies ALL
+    sessions of the rank at once (ei_batch_verify in its wide form: the stacked rows go through the projections as
+    one tcgen05 GEMM, one attention launch serves all sessions); the same rounds with three sessions per forward
+    (the <= 16-row kernels) are timed beside it. The histories are SYNTHETIC: every session's K/V rows are seeded
+    with random BF16 values and adopted (no prefill of 270 000 prompt tokens); the drafts are each session's own
+    greedy continuation from there."""
     syn, sharding = package.synthetic, package.sharding
     total_sessions, stack, k_drafts, p_sub = 64, 3, 4, 0.3
     rows = k_drafts + 1
@@ -407,29 +410,33 @@ def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int):
             session.write_kv(layer, 0, k_rows[:length], v_rows[:length])
         session.adopt_history(length, first)
     del k_rows, v_rows
-    # Greedy continuation of every session by ordinary decoding, 16 sessions per forward.
+    everyone = package.runtime.SessionBatch(sessions)
+    # Greedy continuation of every session, found with forwards of the very shape that is timed below (all
+    # sessions, `rows` rows each, fillers as drafts): a row's bits do not depend on its place in the stack, but
+    # they do depend on the kernels a row count selects, and with random-init weights a last-bit difference is
+    # enough to change a greedy token.
     need = rounds * rows + rows
     continuation = [[first] for first in firsts]
-    for begin in range(0, len(sessions), 16):
-        group = list(range(begin, min(begin + 16, len(sessions))))
-        batch = package.runtime.SessionBatch([sessions[i] for i in group])
-        for _ in range(need):
-            outs = batch.verify([[continuation[i][-1]] for i in group])
-            for i, out in zip(group, outs):
-                continuation[i].append(out.tokens[0])
-        del batch
+    filler = [int(t) for t in syn.make_prompt(13, rows - 1, shape.vocab_size)]
+    while min(len(c) for c in continuation) <= need:
+        outs = everyone.verify([[c[-1]] + filler for c in continuation])
+        for c, out in zip(continuation, outs):
+            c.extend(out.tokens)
     drafts = [syn.corrupt_drafts(1000 + session_id, np.array(c, dtype=np.uint32), p_sub, shape.vocab_size)
               for session_id, c in zip(ids, continuation)]
-    for session, length, first in zip(sessions, lengths, firsts):
-        session.truncate(length)
-        session.set_pending(first)
     groups = [package.runtime.SessionBatch([sessions[i] for i in batch]) for batch in batches]
     pending = list(firsts)
 
-    def run(count: int):
+    def rewind():
+        for i, (session, length, first) in enumerate(zip(sessions, lengths, firsts)):
+            session.truncate(length)
+            session.set_pending(first)
+            pending[i] = first
+
+    def run(count: int, plan, handles):
         emitted_total = 0
         for _ in range(count):
-            for batch, group in zip(batches, groups):
+            for batch, group in zip(plan, handles):
                 inputs = []
                 for i in batch:
                     offset = sessions[i].context_size() - lengths[i]
@@ -439,41 +446,52 @@ def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int):
                     emitted_total += out.emitted
         return emitted_total
 
-    run(2)                                                     # captures the batched graphs
-    for i, (session, length, first) in enumerate(zip(sessions, lengths, firsts)):
-        session.truncate(length)
-        session.set_pending(first)
-        pending[i] = first
-    if dist:
-        dist.barrier()
-    torch.cuda.synchronize()
-    start = time.perf_counter()
-    emitted = run(rounds)
-    torch.cuda.synchronize()
-    elapsed_ms = (time.perf_counter() - start) * 1e3
-    if dist:
-        dist.barrier()
-    session_steps = rounds * len(sessions)
-    forwards = rounds * len(batches)
+    def timed(count: int, plan, handles):
+        rewind()
+        run(2, plan, handles)                                  # warms (and, for the narrow form, captures the graphs)
+        rewind()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start = time.perf_counter()
+        emitted = run(count, plan, handles)
+        torch.cuda.synchronize()
+        elapsed_ms = (time.perf_counter() - start) * 1e3
+        if dist:
+            dist.barrier()
+        return emitted, elapsed_ms
+
     kv_per_token = 2 * shape.n_layers * kv_width * 2
-    bytes_moved = forwards * model.weight_bytes() + rounds * sum(lengths) * kv_per_token
-    totals, times = sharding.aggregate(dist, torch, [emitted, session_steps, forwards, bytes_moved], [elapsed_ms], "cuda")
-    del groups, sessions, model
+    narrow_rounds = max(2, rounds // 6)
+    narrow_emitted, narrow_ms = timed(narrow_rounds, batches, groups)
+    emitted, elapsed_ms = timed(rounds, [list(range(len(sessions)))], [everyone])
+    session_steps = rounds * len(sessions)
+    bytes_moved = rounds * model.weight_bytes() + rounds * sum(lengths) * kv_per_token
+    totals, times = sharding.aggregate(dist, torch, [emitted, session_steps, rounds, bytes_moved, narrow_emitted,
+                                                     narrow_rounds * len(sessions), narrow_rounds * len(batches)],
+                                       [elapsed_ms, narrow_ms], "cuda")
+    del groups, everyone, sessions, model
     torch.cuda.empty_cache()
     peak, peak_kind = measured_peaks()
     achieved = totals[3] / (times[0] * 1e-3) / 1e9 / world
     return {
         "workload": ("qwen2.5-7b-shape AWQ (28 layers, hidden 3584, 28Q/4KV, q/k/v bias, FFN 18944, vocab 152064), "
-                     "64 sessions, seeded prompt lengths in [256, 8192], k=4 (5 rows), p=0.3, 3 sessions per forward"),
+                     "64 sessions, seeded prompt lengths in [256, 8192], k=4 (5 rows), p=0.3, all sessions of a GPU "
+                     "per forward"),
         "history": "synthetic: K/V rows seeded with random BF16 values and adopted (no prompt prefill)",
         "sessions_total": total_sessions, "sessions_per_gpu": [len(sharding.session_shard(total_sessions, world, r))
                                                                  for r in range(world)],
         "rounds": rounds, "accepted_tokens_per_s": sharding.throughput(totals[0], times[0]),
         "session_steps_per_s": sharding.throughput(totals[1], times[0]),
         "tokens_per_session_step": totals[0] / totals[1], "ms_per_forward": times[0] * world / totals[2],
+        "stacked_rows_per_forward": rows * len(ids),
         "timing": "host clock around the rounds (one host synchronisation per forward), maximum over ranks",
         "step_roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                           "peak_source": peak_kind, "note": "per GPU: weights once per forward + the live KV of its sessions"},
+        "three_sessions_per_forward": {"rounds": narrow_rounds,
+                                       "accepted_tokens_per_s": sharding.throughput(totals[4], times[1]),
+                                       "session_steps_per_s": sharding.throughput(totals[5], times[1]),
+                                       "ms_per_forward": times[1] * world / totals[6]},
     }
 
 

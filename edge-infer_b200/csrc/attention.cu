@@ -69,9 +69,12 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   extern __shared__ __align__(128) unsigned char smem[];
   // The context length was written by the previous step; the preceding kernel of this step only appends the
   // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
-  const int first_offset = p.device_offset ? *p.device_offset : p.host_offset;
+  // Wide batch (split form only): grid slice z is a session with its own cache, context length, queries, scratch.
+  const SessionSlot* owner = (!kDirect && p.slots) ? p.slots + blockIdx.z : nullptr;
+  const int capacity = owner ? owner->capacity : p.capacity;
+  const int first_offset = owner ? owner->control->context : (p.device_offset ? *p.device_offset : p.host_offset);
   const int kv_head = blockIdx.y;
-  if (first_offset < 0 || first_offset + p.rows > p.capacity) {
+  if (first_offset < 0 || first_offset + p.rows > capacity) {
     // The whole grid leaves: it still waits for its predecessor first, so that a successor never sees this
     // kernel complete before the kernels ahead of it have.
     grid_dependency_wait();
@@ -91,8 +94,11 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
 
   unsigned char* k_smem[2] = {smem, smem + 2 * kTileBytes};
   unsigned char* v_smem[2] = {smem + kTileBytes, smem + 3 * kTileBytes};
-  const bf16* k_base = p.k + size_t(kv_head) * kDim;
-  const bf16* v_base = p.v + size_t(kv_head) * kDim;
+  const size_t layer_offset = owner ? size_t(p.layer) * size_t(capacity) * p.kv_stride : 0;
+  const bf16* k_base = (owner ? owner->k_cache + layer_offset : p.k) + size_t(kv_head) * kDim;
+  const bf16* v_base = (owner ? owner->v_cache + layer_offset : p.v) + size_t(kv_head) * kDim;
+  const bf16* q_base = p.q + (owner ? size_t(blockIdx.z) * p.rows * p.q_stride : 0);
+  float* scratch = p.scratch + (owner ? size_t(blockIdx.z) * p.scratch_stride : 0);
 
   const bool settled = end <= offset;  // no row of this chunk is written by the preceding kernel
   if (!settled) grid_dependency_wait();
@@ -111,8 +117,8 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   const int h_hi = kv_head * group + (live_hi ? i_hi % group : 0);
   uint32_t qa[8][4];
   {
-    const bf16* q_lo = p.q + size_t(first_row + r_lo) * p.q_stride + size_t(h_lo) * kDim;
-    const bf16* q_hi = p.q + size_t(first_row + r_hi) * p.q_stride + size_t(h_hi) * kDim;
+    const bf16* q_lo = q_base + size_t(first_row + r_lo) * p.q_stride + size_t(h_lo) * kDim;
+    const bf16* q_hi = q_base + size_t(first_row + r_hi) * p.q_stride + size_t(h_hi) * kDim;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
       qa[kk][0] = live_lo ? *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 2 * c) : 0u;
@@ -241,7 +247,7 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   }
   const size_t slots = size_t(p.rows) * p.heads;
   if (live_lo) {
-    float* dst = p.scratch + (size_t(split) * slots + size_t(r_lo) * p.heads + h_lo) * kPartial;
+    float* dst = scratch + (size_t(split) * slots + size_t(r_lo) * p.heads + h_lo) * kPartial;
 #pragma unroll
     for (int d = 0; d < 16; ++d) *reinterpret_cast<float2*>(dst + d * 8 + 2 * c) = make_float2(o[d][0], o[d][1]);
     if (c == 0) {
@@ -250,7 +256,7 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
     }
   }
   if (live_hi) {
-    float* dst = p.scratch + (size_t(split) * slots + size_t(r_hi) * p.heads + h_hi) * kPartial;
+    float* dst = scratch + (size_t(split) * slots + size_t(r_hi) * p.heads + h_hi) * kPartial;
 #pragma unroll
     for (int d = 0; d < 16; ++d) *reinterpret_cast<float2*>(dst + d * 8 + 2 * c) = make_float2(o[d][2], o[d][3]);
     if (c == 0) {
@@ -270,14 +276,17 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   __shared__ float4 partial_out[4][32];
   // The context length was written by the previous step (or by the host): it does not come from the kernel
   // this one waits for, so it is read first and the wait hides its latency.
-  const int offset = p.device_offset ? *p.device_offset : p.host_offset;
+  const SessionSlot* owner = p.slots ? p.slots + blockIdx.y : nullptr;
+  const int offset = owner ? owner->control->context : (p.device_offset ? *p.device_offset : p.host_offset);
   grid_dependency_wait();
   grid_launch_dependents();
   const int slot = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = p.rows * p.heads;
   const int length = offset + p.rows;
-  if (offset < 0 || length > p.capacity) return;  // after the wait above
+  if (offset < 0 || length > (owner ? owner->capacity : p.capacity)) return;  // after the wait above
+  const float* scratch = p.scratch + (owner ? size_t(blockIdx.y) * p.scratch_stride : 0);
+  bf16* out = p.out + (owner ? size_t(blockIdx.y) * p.rows * p.out_stride : 0);
   const int splits = min(64, (length + p.chunk - 1) / p.chunk);
   // This warp's splits (w, w + 4, ...) are requested together with the maxima and sums, so that the block pays
   // one trip to memory instead of two.
@@ -287,11 +296,11 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
     const int s = warp + 4 * i;
     values[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (s < splits)
-      values[i] = *reinterpret_cast<const float4*>(p.scratch + (size_t(s) * slots + slot) * kPartial + 4 * lane);
+      values[i] = *reinterpret_cast<const float4*>(scratch + (size_t(s) * slots + slot) * kPartial + 4 * lane);
   }
   float m = -INFINITY, l = 0.0f;
   if (int(threadIdx.x) < splits) {
-    const float* src = p.scratch + (size_t(threadIdx.x) * slots + slot) * kPartial;
+    const float* src = scratch + (size_t(threadIdx.x) * slots + slot) * kPartial;
     m = src[128];
     l = src[129];
   }
@@ -323,7 +332,7 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   const float4 a = partial_out[0][lane], b = partial_out[1][lane], c = partial_out[2][lane], d = partial_out[3][lane];
   const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
   const int row = slot / p.heads, head = slot - row * p.heads;
-  bf16* dst = p.out + size_t(row) * p.out_stride + size_t(head) * kDim + 4 * lane;
+  bf16* dst = out + size_t(row) * p.out_stride + size_t(head) * kDim + 4 * lane;
   uint2 packed;
   packed.x = pack_bf16(((a.x + b.x) + (c.x + d.x)) * inverse, ((a.y + b.y) + (c.y + d.y)) * inverse);
   packed.y = pack_bf16(((a.z + b.z) + (c.z + d.z)) * inverse, ((a.w + b.w) + (c.w + d.w)) * inverse);
@@ -363,9 +372,10 @@ void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool
   const int group = p.heads / p.kv_heads;
   const int warps = (p.rows * group + 15) / 16;
   configure_attention_kernels();
-  launch(verify_attention_kernel<false>, dim3(p.max_splits, p.kv_heads), dim3(warps * 32), size_t(4 * kTileBytes),
-         stream, pdl, p);
-  launch(attention_merge_kernel, dim3(p.rows * p.heads), dim3(128), 0, stream, pdl, p);
+  const unsigned sessions = p.slots ? unsigned(p.sessions) : 1u;
+  launch(verify_attention_kernel<false>, dim3(p.max_splits, p.kv_heads, sessions), dim3(warps * 32),
+         size_t(4 * kTileBytes), stream, pdl, p);
+  launch(attention_merge_kernel, dim3(p.rows * p.heads, sessions), dim3(128), 0, stream, pdl, p);
 }
 
 void launch_prompt_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {

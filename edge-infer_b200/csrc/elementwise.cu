@@ -135,19 +135,28 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
   grid_dependency_wait();
   const int row = blockIdx.x;
   if (threadIdx.x == 0) {
+    Control* control = p.control;
+    int local = row, step_rows = p.rows, capacity = p.capacity;
+    if (p.slots) {
+      const int session = row / p.rows_per_session;
+      local = row - session * p.rows_per_session;
+      step_rows = p.rows_per_session;
+      control = p.slots[session].control;
+      capacity = p.slots[session].capacity;
+    }
     uint32_t token;
     if (p.tokens) {
       token = p.tokens[row];
-    } else if (row == 0) {
-      token = p.control->pending;
+    } else if (local == 0) {
+      token = control->pending;
     } else {
       const DraftSource source = *p.source;
-      const long long index = (long long)p.control->context + row - source.base;
+      const long long index = (long long)control->context + local - source.base;
       token = (source.drafts && index >= 0 && index < source.count) ? source.drafts[index] : 0u;
     }
     p.step_tokens[row] = token;
-    if (token >= uint32_t(p.vocab)) atomicOr(&p.control->status, 2);
-    if (row == 0 && p.control->context + p.rows > p.capacity) atomicOr(&p.control->status, 1);
+    if (token >= uint32_t(p.vocab)) atomicOr(&control->status, 2);
+    if (local == 0 && control->context + step_rows > capacity) atomicOr(&control->status, 1);
     token_shared = token;
   }
   __syncthreads();
@@ -208,9 +217,23 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams
   const int row = warp_global / per_row, slot = warp_global - row * per_row;
   // Read before waiting for the projection: the context length (written by the previous step), the norm
   // weights and the rotation table do not come from it, so their latency overlaps its tail.
-  const int context = p.control->context;
-  const int position = context + row;
-  if (context + p.rows > p.capacity || position >= p.max_positions) {  // status set by the embed kernel
+  const Control* control = p.control;
+  bf16 *k_cache = p.k_cache, *v_cache = p.v_cache;
+  int local = row, step_rows = p.rows, capacity = p.capacity;
+  if (p.slots) {
+    const int session = row / p.rows_per_session;
+    const SessionSlot owner = p.slots[session];
+    local = row - session * p.rows_per_session;
+    step_rows = p.rows_per_session;
+    control = owner.control;
+    capacity = owner.capacity;
+    const size_t layer_offset = size_t(p.layer) * size_t(capacity) * p.kv_heads * 128;
+    k_cache = owner.k_cache + layer_offset;
+    v_cache = owner.v_cache + layer_offset;
+  }
+  const int context = control->context;
+  const int position = context + local;
+  if (context + step_rows > capacity || position >= p.max_positions) {  // status set by the embed kernel
     grid_dependency_wait();  // every block leaves here: complete only after the predecessor has
     return;
   }
@@ -232,7 +255,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams
   if (is_value) {  // value head: append as is
     const int kvh = slot - p.heads - p.kv_heads;
     const uint2 v = *reinterpret_cast<const uint2*>(head + lane * 4);
-    *reinterpret_cast<uint2*>(p.v_cache + (size_t(position) * p.kv_heads + kvh) * 128 + lane * 4) = v;
+    *reinterpret_cast<uint2*>(v_cache + (size_t(position) * p.kv_heads + kvh) * 128 + lane * 4) = v;
     return;
   }
   const uint32_t lo = *reinterpret_cast<const uint32_t*>(head + 2 * lane);
@@ -253,7 +276,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const QkvParams
     *reinterpret_cast<uint32_t*>(head + 2 * lane) = out_lo;
     *reinterpret_cast<uint32_t*>(head + 64 + 2 * lane) = out_hi;
   } else {
-    bf16* dst = p.k_cache + (size_t(position) * p.kv_heads + (slot - p.heads)) * 128;
+    bf16* dst = k_cache + (size_t(position) * p.kv_heads + (slot - p.heads)) * 128;
     *reinterpret_cast<uint32_t*>(dst + 2 * lane) = out_lo;
     *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = out_hi;
   }

@@ -16,6 +16,16 @@ struct Control {
   ei_verify_result last;
 };
 
+// One session of a wide batch (more than 16 stacked rows): where its device state lives. Kernels of the wide
+// step take an array of these and find their session from the stacked row (or a grid dimension).
+struct SessionSlot {
+  Control* control;
+  bf16* k_cache;  // layer 0; layer l at k_cache + l * capacity * kv_heads * 128
+  bf16* v_cache;
+  int capacity;
+  int reserved;
+};
+
 // ---- elementwise.cu ----
 void launch_rms_norm(const bf16* in, const bf16* weight, bf16* out, size_t rows, size_t width, float eps,
                      cudaStream_t stream, bool pdl);
@@ -56,6 +66,8 @@ struct EmbedParams {
   float eps;
   bf16* residual;           // [rows, hidden]
   bf16* normed;             // [rows, hidden]
+  const SessionSlot* slots; // wide batch: stacked row r belongs to session r / rows_per_session (control and
+  int rows_per_session;     // capacity above are then unused; rows = all stacked rows; tokens must be given)
 };
 // Token selection + embedding lookup + first RMSNorm, one block per row.
 void launch_embed_norm(const EmbedParams& p, cudaStream_t stream, bool pdl);
@@ -72,6 +84,8 @@ struct QkvParams {
   int capacity;
   bf16* k_cache;            // [capacity, kv_heads * 128] of this layer
   bf16* v_cache;
+  const SessionSlot* slots; // wide batch, as in EmbedParams; the caches are the slots' at `layer`
+  int rows_per_session, layer;
 };
 // Per-head QK RMSNorm + RoPE + KV append at the device-side context length, one warp per (row, head).
 void launch_qk_norm_rope_store(const QkvParams& p, cudaStream_t stream, bool pdl);
@@ -104,6 +118,9 @@ struct AttentionParams {
   float* scratch;           // [max_splits][rows * heads][132]
   bf16* out;                // row r, head h at out + r * out_stride + h * 128
   int out_stride;
+  const SessionSlot* slots; // wide batch: one grid slice per session (`sessions` of them), `rows` query rows
+  int sessions, layer;      // each; session j reads q + j * rows * q_stride, its own cache and context length,
+  size_t scratch_stride;    // scratch + j * scratch_stride (floats), and writes out + j * rows * out_stride
 };
 int attention_chunk_for(size_t kv_length);
 size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length);
@@ -128,6 +145,13 @@ void launch_finalize(const float* best_value, const int* best_index, int parts, 
 // Makes a draft session continue from where the target session stands: copies context length and pending token
 // and inherits a raised status. One thread.
 void launch_adopt_control(Control* mine, const Control* theirs, cudaStream_t stream);
+// Wide batch: per-row argmax partials laid out [row][parts] for any number of rows, then per session the final
+// argmax of its rows, acceptance against step_tokens and commit in its slot's control block.
+void launch_argmax_partials_wide(const bf16* logits, size_t rows, size_t vocab, size_t row_stride, float* best_value,
+                                 int* best_index, int parts, cudaStream_t stream, bool pdl);
+void launch_finalize_wide(const float* best_value, const int* best_index, int parts, int rows_per_session,
+                          int sessions, uint32_t* targets, const uint32_t* step_tokens, const SessionSlot* slots,
+                          cudaStream_t stream, bool pdl);
 
 // Acceptance only, from targets already chosen.
 void launch_accept(const uint32_t* inputs, const uint32_t* targets, int rows, int32_t* context_length,

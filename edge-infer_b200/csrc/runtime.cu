@@ -48,6 +48,13 @@ __global__ void commit_rows_kernel(Control* control, int rows) {
   control->context += rows;
 }
 
+// Copies the control block of every session of a wide batch into one array (read back with one copy).
+__global__ void gather_controls_kernel(const SessionSlot* slots, int count, Control* out) {
+  grid_dependency_wait();
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < count) out[j] = *slots[j].control;
+}
+
 __global__ void silu_pair_rows_kernel(const bf16* gate_up, int rows, int ffn, bf16* out) {
   grid_dependency_wait();
   const int total = rows * ffn;
@@ -325,7 +332,22 @@ struct ei_session {
 struct ei_batch {
   std::vector<ei_session*> sessions;
   cudaGraphExec_t graphs[kMaxRows + 1] = {};  // by rows per session
+  // Wide form (more than 16 stacked rows): the sessions' slots on the device, and buffers sized on first use
+  // for sessions * rows stacked rows.
+  SessionSlot* slots = nullptr;
+  unsigned char* wide_arena = nullptr;
+  size_t wide_rows = 0;
+  bf16* logits = nullptr;           // [stacked rows, vocab]
+  float* attention_scratch = nullptr;
+  size_t scratch_stride = 0;        // floats per session
+  float* best_value = nullptr;      // [stacked rows][kWideParts]
+  int* best_index = nullptr;
+  uint32_t* targets = nullptr;      // [stacked rows]
+  Control* controls = nullptr;      // [sessions] gathered after a step
+  Control* host_controls = nullptr; // pinned
 };
+constexpr int kWideParts = 8;       // argmax partials per row of the wide form
+constexpr size_t kMaxBatchSessions = 1024;
 
 // A target session and a draft session that generate together without host round trips: per round the draft
 // session decodes drafts_per_round + 1 tokens, each from the token the previous step left on the device, the
@@ -560,6 +582,23 @@ void run_prompt_linear(ei_session& s, const PreparedLinear& w, const bf16* x, in
   launch_prompt_gemm(w.quantized, p, s.stream, pdl);
 }
 
+// A projection with a BF16 output over all rows of a segment. Few output tiles (the q|k|v projection of a short
+// segment) would leave most SMs idle: K is then split over blocks that leave FP32 sums, and a second kernel adds
+// them, joins the bias and rounds once.
+void run_prompt_linear_store(ei_session& s, const PreparedLinear& w, const bf16* x, int rows, bf16* out, bool pdl) {
+  ei_model& m = *s.model;
+  auto& ws = m.prompt;
+  const int ksplit = w.out % 4 == 0 ? prompt_gemm_ksplit(rows, w.out, w.in, m.multiprocessors, ws.partial_bytes) : 1;
+  if (ksplit < 2) {
+    run_prompt_linear(s, w, x, rows, out, pdl);
+    return;
+  }
+  run_prompt_linear(s, w, x, rows, nullptr, pdl, ksplit);
+  tick(s);
+  launch(splitk_store_kernel, dim3(std::min(m.multiprocessors * 8, (rows * w.out + 255) / 256)), dim3(256), 0, s.stream,
+         pdl, (const float*)ws.partial, ksplit, rows, w.out, w.bias, out, w.out);
+}
+
 // projection -> residual add -> RMSNorm over all rows of a segment: the projection leaves FP32 sums (K split
 // over blocks when few token tiles would leave SMs idle) that the residual + norm kernel finishes, as in the
 // verify step.
@@ -622,7 +661,7 @@ void enqueue_prompt_segment(ei_session& s, int rows, bool head) {
   const int elementwise_blocks = m.multiprocessors * 8;
   for (size_t layer = 0; layer < m.layers.size(); ++layer) {
     const auto& L = m.layers[layer];
-    run_prompt_linear(s, L.qkv, ws.normed, rows, ws.qkv, pdl);
+    run_prompt_linear_store(s, L.qkv, ws.normed, rows, ws.qkv, pdl);
     QkvParams q{};
     q.qkv = ws.qkv;
     q.rows = rows;
@@ -948,6 +987,137 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
     launch_finalize(lead.best_value + j * rows, lead.best_index + j * rows, parts, rows, lead.targets + j * rows,
                     lead.step_tokens + j * rows, s.control, nullptr, nullptr, nullptr, lead.stream, pdl);
   }
+}
+
+void ensure_wide_buffers(ei_batch& batch, size_t rows) {
+  ei_session& lead = *batch.sessions[0];
+  const auto& c = lead.model->config;
+  const size_t count = batch.sessions.size(), total = count * rows;
+  if (batch.wide_arena && batch.wide_rows >= total) return;
+  if (batch.wide_arena) {
+    EI_CUDA(cudaStreamSynchronize(lead.stream));
+    cudaFree(batch.wide_arena);
+    batch.wide_arena = nullptr;
+  }
+  // Split partials for the sessions' full capacity and 16 rows each, so that a later call with more rows per
+  // session only regrows the row-sized buffers.
+  const size_t scratch_stride = attention_scratch_bytes(kMaxRows, c.n_heads, lead.capacity) / sizeof(float);
+  size_t offset = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = offset;
+    offset += aligned(bytes);
+    return at;
+  };
+  const size_t o_logits = take(total * c.vocab_size * 2), o_scratch = take(count * scratch_stride * sizeof(float));
+  const size_t o_value = take(total * kWideParts * sizeof(float)), o_index = take(total * kWideParts * sizeof(int));
+  const size_t o_targets = take(total * 4), o_controls = take(count * sizeof(Control));
+  EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&batch.wide_arena), offset));
+  unsigned char* base = batch.wide_arena;
+  batch.logits = reinterpret_cast<bf16*>(base + o_logits);
+  batch.attention_scratch = reinterpret_cast<float*>(base + o_scratch);
+  batch.scratch_stride = scratch_stride;
+  batch.best_value = reinterpret_cast<float*>(base + o_value);
+  batch.best_index = reinterpret_cast<int*>(base + o_index);
+  batch.targets = reinterpret_cast<uint32_t*>(base + o_targets);
+  batch.controls = reinterpret_cast<Control*>(base + o_controls);
+  batch.wide_rows = total;
+}
+
+// One verify step of every session of the batch in the wide form: the stacked rows (any number up to the
+// prompt workspace's) go through every projection as one tcgen05 GEMM, so the weights are read once for all
+// sessions; embedding, norm / RoPE / KV append, attention, greedy choice, acceptance and commit run as single
+// launches that find each row's session in the slot array. Runs on the leader's stream and the model's prompt
+// workspace.
+void enqueue_wide_batch_step(ei_batch& batch, int rows) {
+  ei_session& lead = *batch.sessions[0];
+  ei_model& m = *lead.model;
+  auto& ws = m.prompt;
+  const auto& c = m.config;
+  const int count = int(batch.sessions.size()), total = count * rows;
+  const int heads = int(c.n_heads), kv_heads = int(c.n_kv_heads), hidden = int(c.hidden_size), ffn = int(c.intermediate_size);
+  const int qkv_width = (heads + 2 * kv_heads) * 128, kv_width = kv_heads * 128;
+  const bool pdl = true;
+
+  EmbedParams e{};
+  e.tokens = ws.tokens;
+  e.step_tokens = ws.step_tokens;
+  e.table = m.embedding;
+  e.vocab = int(c.vocab_size);
+  e.hidden = hidden;
+  e.rows = total;
+  e.norm_weight = m.layers[0].attention_norm;
+  e.eps = c.rms_norm_eps;
+  e.residual = ws.residual;
+  e.normed = ws.normed;
+  e.slots = batch.slots;
+  e.rows_per_session = rows;
+  tick(lead);
+  launch_embed_norm(e, lead.stream, false);
+
+  for (size_t layer = 0; layer < m.layers.size(); ++layer) {
+    const auto& L = m.layers[layer];
+    run_prompt_linear_store(lead, L.qkv, ws.normed, total, ws.qkv, pdl);
+    QkvParams q{};
+    q.qkv = ws.qkv;
+    q.rows = total;
+    q.heads = heads;
+    q.kv_heads = kv_heads;
+    q.qkv_stride = qkv_width;
+    q.q_norm = c.qk_norm ? L.q_norm : nullptr;
+    q.k_norm = c.qk_norm ? L.k_norm : nullptr;
+    q.eps = c.rms_norm_eps;
+    q.rope_table = m.rope_table;
+    q.max_positions = int(c.max_position_embeddings);
+    q.slots = batch.slots;
+    q.rows_per_session = rows;
+    q.layer = int(layer);
+    tick(lead);
+    launch_qk_norm_rope_store(q, lead.stream, pdl);
+
+    AttentionParams a{};
+    a.q = ws.qkv;
+    a.q_stride = qkv_width;
+    a.kv_stride = kv_width;
+    a.rows = rows;
+    a.heads = heads;
+    a.kv_heads = kv_heads;
+    // Many sessions fill the GPU by themselves: longer chunks than the single-session step's (fewer partials to
+    // write and merge, the per-block set-up paid once per eight tiles), still at most 64 splits.
+    a.chunk = std::max(512, lead.attention_chunk);
+    a.max_splits = int((lead.capacity + a.chunk - 1) / a.chunk);
+    a.scratch = batch.attention_scratch;
+    a.scratch_stride = batch.scratch_stride;
+    a.out = ws.attention;
+    a.out_stride = heads * 128;
+    a.slots = batch.slots;
+    a.sessions = count;
+    a.layer = int(layer);
+    tick(lead);
+    tick(lead);
+    launch_verify_attention(a, lead.stream, pdl);
+
+    run_prompt_projection_residual_norm(lead, L.o, ws.attention, total, L.ffn_norm, pdl);
+    run_prompt_linear(lead, L.gate_up, ws.normed, total, ws.gate_up, pdl);
+    tick(lead);
+    if (ffn % 8 == 0)
+      launch(silu_pair_rows_vec_kernel, dim3(m.multiprocessors * 8), dim3(256), 0, lead.stream, pdl,
+             (const bf16*)ws.gate_up, total, ffn, ws.act);
+    else
+      launch(silu_pair_rows_kernel, dim3(m.multiprocessors * 8), dim3(256), 0, lead.stream, pdl,
+             (const bf16*)ws.gate_up, total, ffn, ws.act);
+    const bf16* next_norm = layer + 1 < m.layers.size() ? m.layers[layer + 1].attention_norm : m.output_norm;
+    run_prompt_projection_residual_norm(lead, L.down, ws.act, total, next_norm, pdl);
+  }
+  run_prompt_linear(lead, m.lm_head, ws.normed, total, batch.logits, pdl);
+  tick(lead);
+  launch_argmax_partials_wide(batch.logits, total, c.vocab_size, c.vocab_size, batch.best_value, batch.best_index,
+                              kWideParts, lead.stream, pdl);
+  tick(lead);
+  launch_finalize_wide(batch.best_value, batch.best_index, kWideParts, rows, count, batch.targets, ws.step_tokens,
+                       batch.slots, lead.stream, pdl);
+  tick(lead);
+  launch(gather_controls_kernel, dim3((count + 127) / 128), dim3(128), 0, lead.stream, pdl,
+         (const SessionSlot*)batch.slots, count, batch.controls);
 }
 
 void submit_batch_step(ei_batch& batch, int rows) {
@@ -1336,7 +1506,8 @@ ei_status ei_session_verify(ei_session* session, const uint32_t* host_tokens, si
 
 ei_status ei_batch_create(ei_session* const* sessions, size_t count, ei_batch** out) {
   return guarded([&] {
-    if (!sessions || !count || count > kMaxRows || !out) throw std::invalid_argument("A batch takes 1..16 sessions");
+    if (!sessions || !count || count > kMaxBatchSessions || !out)
+      throw std::invalid_argument("A batch takes 1..1024 sessions");
     auto batch = std::make_unique<ei_batch>();
     for (size_t j = 0; j < count; ++j) {
       ei_session* s = sessions[j];
@@ -1348,6 +1519,16 @@ ei_status ei_batch_create(ei_session* const* sessions, size_t count, ei_batch** 
         if (sessions[i] == s) throw std::invalid_argument("A session appears twice in the batch");
       batch->sessions.push_back(s);
     }
+    require_device(*sessions[0]);
+    std::vector<SessionSlot> slots(count);
+    for (size_t j = 0; j < count; ++j)
+      slots[j] = SessionSlot{sessions[j]->control, sessions[j]->k_cache, sessions[j]->v_cache, int(sessions[j]->capacity), 0};
+    EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&batch->slots), count * sizeof(SessionSlot)));
+    if (cudaMemcpy(batch->slots, slots.data(), count * sizeof(SessionSlot), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void**>(&batch->host_controls), count * sizeof(Control)) != cudaSuccess) {
+      cudaFree(batch->slots);
+      throw std::runtime_error("Batch state could not be placed on the device");
+    }
     *out = batch.release();
   });
 }
@@ -1356,6 +1537,10 @@ void ei_batch_destroy(ei_batch* batch) {
   if (!batch) return;
   for (auto& exec : batch->graphs)
     if (exec) cudaGraphExecDestroy(exec);
+  if (!batch->sessions.empty()) cudaStreamSynchronize(batch->sessions[0]->stream);
+  if (batch->slots) cudaFree(batch->slots);
+  if (batch->wide_arena) cudaFree(batch->wide_arena);
+  if (batch->host_controls) cudaFreeHost(batch->host_controls);
   delete batch;
 }
 
@@ -1363,9 +1548,14 @@ ei_status ei_batch_verify(ei_batch* batch, const uint32_t* host_tokens, size_t r
   return guarded([&] {
     if (!batch) throw std::invalid_argument("batch is null");
     const size_t count = batch->sessions.size();
-    if (!host_tokens || !results || !rows || rows * count > kMaxRows)
-      throw std::invalid_argument("A batched verify takes sessions * rows <= 16 tokens and one result per session");
     ei_session& lead = *batch->sessions[0];
+    const bool wide = rows * count > kMaxRows;
+    const size_t room = lead.model->prompt_ready && prompt_linear_ok(lead.model->lm_head)
+                            ? std::min<size_t>(kPromptSegment, lead.model->config.max_position_embeddings) : kMaxRows;
+    if (!host_tokens || !results || !rows || rows > kMaxRows || rows * count > room)
+      throw std::invalid_argument(
+          "A batched verify takes 1..16 rows per session, one result per session, and sessions * rows <= 16 stacked "
+          "rows - or <= 2048 for models whose projections the prompt GEMM takes");
     require_device(lead);
     const size_t vocab = lead.model->config.vocab_size;
     for (ei_session* s : batch->sessions) {
@@ -1375,15 +1565,32 @@ ei_status ei_batch_verify(ei_batch* batch, const uint32_t* host_tokens, size_t r
     }
     for (size_t i = 0; i < rows * count; ++i)
       if (host_tokens[i] >= vocab) throw std::invalid_argument("Token exceeds vocabulary");
+    // The wide form borrows the model's prompt workspace until the leader's stream has drained.
+    std::unique_lock<std::mutex> workspace(lead.model->prompt.mutex, std::defer_lock);
+    if (wide) workspace.lock();
     try {
       // Work queued on the other sessions' own streams must be done before the shared step touches their state.
       for (size_t j = 1; j < count; ++j) synchronize(*batch->sessions[j]);
-      std::memcpy(lead.host_tokens, host_tokens, rows * count * 4);
-      EI_CUDA(cudaMemcpyAsync(lead.tokens, lead.host_tokens, rows * count * 4, cudaMemcpyHostToDevice, lead.stream));
-      submit_batch_step(*batch, int(rows));
-      for (ei_session* s : batch->sessions)
-        EI_CUDA(cudaMemcpyAsync(s->host_control, s->control, sizeof(Control), cudaMemcpyDeviceToHost, lead.stream));
-      synchronize(lead);
+      if (wide) {
+        ensure_prompt_workspace(*lead.model);
+        ensure_wide_buffers(*batch, rows);
+        auto& ws = lead.model->prompt;
+        synchronize(lead);  // the pinned staging buffers are reused by every call
+        std::memcpy(ws.host_tokens, host_tokens, rows * count * 4);
+        EI_CUDA(cudaMemcpyAsync(ws.tokens, ws.host_tokens, rows * count * 4, cudaMemcpyHostToDevice, lead.stream));
+        enqueue_wide_batch_step(*batch, int(rows));
+        EI_CUDA(cudaMemcpyAsync(batch->host_controls, batch->controls, count * sizeof(Control), cudaMemcpyDeviceToHost,
+                                lead.stream));
+        synchronize(lead);
+        for (size_t j = 0; j < count; ++j) *batch->sessions[j]->host_control = batch->host_controls[j];
+      } else {
+        std::memcpy(lead.host_tokens, host_tokens, rows * count * 4);
+        EI_CUDA(cudaMemcpyAsync(lead.tokens, lead.host_tokens, rows * count * 4, cudaMemcpyHostToDevice, lead.stream));
+        submit_batch_step(*batch, int(rows));
+        for (ei_session* s : batch->sessions)
+          EI_CUDA(cudaMemcpyAsync(s->host_control, s->control, sizeof(Control), cudaMemcpyDeviceToHost, lead.stream));
+        synchronize(lead);
+      }
       for (ei_session* s : batch->sessions) s->context = size_t(s->host_control->context);
       for (ei_session* s : batch->sessions)
         if (s->host_control->status) {

@@ -20,6 +20,8 @@ __device__ __forceinline__ void take_better(float& best, int& index, float value
   }
 }
 
+// kWide: partials laid out [row][parts] for any number of rows; otherwise [part][16] for at most 16 rows.
+template <bool kWide>
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(const bf16* logits, int vocab,
                                                                         size_t row_stride, float* best_value,
                                                                         int* best_index) {
@@ -75,8 +77,9 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(const bf
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int w = 1; w < kArgmaxThreads / 32; ++w) take_better(best, index, values[w], indices[w]);
-    best_value[blockIdx.x * 16 + row] = best;
-    best_index[blockIdx.x * 16 + row] = index;
+    const size_t at = kWide ? size_t(row) * gridDim.x + blockIdx.x : size_t(blockIdx.x) * 16 + row;
+    best_value[at] = best;
+    best_index[at] = index;
   }
 }
 
@@ -158,6 +161,34 @@ __global__ void __launch_bounds__(512) finalize_kernel(const float* best_value, 
   accept_commit(chosen, rows, step_tokens, control, context_length, pending, result, sink);
 }
 
+// Wide batch: one block per session, one warp per row of that session. Partials are laid out [row][parts].
+__global__ void __launch_bounds__(512) finalize_wide_kernel(const float* best_value, const int* best_index, int parts,
+                                                            int rows, uint32_t* targets, const uint32_t* step_tokens,
+                                                            const SessionSlot* slots) {
+  __shared__ uint32_t chosen[16];
+  grid_dependency_wait();
+  const int session = blockIdx.x, row = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (row < rows) {
+    const size_t base = (size_t(session) * rows + row) * parts;
+    float best = -INFINITY;
+    int index = 0x7fffffff;
+    for (int part = lane; part < parts; part += 32) take_better(best, index, best_value[base + part], best_index[base + part]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_index = __shfl_xor_sync(0xffffffffu, index, o);
+      take_better(best, index, other, other_index);
+    }
+    if (lane == 0) {
+      chosen[row] = index == 0x7fffffff ? 0u : uint32_t(index);
+      targets[size_t(session) * rows + row] = chosen[row];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  accept_commit(chosen, rows, step_tokens + size_t(session) * rows, slots[session].control, nullptr, nullptr, nullptr);
+}
+
 __global__ void adopt_control_kernel(Control* mine, const Control* theirs) {
   if (threadIdx.x || blockIdx.x) return;
   mine->context = theirs->context;
@@ -174,8 +205,21 @@ int sample_partial_blocks(size_t vocabulary, int multiprocessors) {
 
 void launch_argmax_partials(const bf16* logits, size_t rows, size_t vocab, size_t row_stride, float* best_value,
                             int* best_index, int blocks, cudaStream_t stream, bool pdl) {
-  launch(argmax_partial_kernel, dim3(blocks, unsigned(rows)), dim3(kArgmaxThreads), 0, stream, pdl, logits,
+  launch(argmax_partial_kernel<false>, dim3(blocks, unsigned(rows)), dim3(kArgmaxThreads), 0, stream, pdl, logits,
          int(vocab), row_stride, best_value, best_index);
+}
+
+void launch_argmax_partials_wide(const bf16* logits, size_t rows, size_t vocab, size_t row_stride, float* best_value,
+                                 int* best_index, int parts, cudaStream_t stream, bool pdl) {
+  launch(argmax_partial_kernel<true>, dim3(parts, unsigned(rows)), dim3(kArgmaxThreads), 0, stream, pdl, logits,
+         int(vocab), row_stride, best_value, best_index);
+}
+
+void launch_finalize_wide(const float* best_value, const int* best_index, int parts, int rows_per_session,
+                          int sessions, uint32_t* targets, const uint32_t* step_tokens, const SessionSlot* slots,
+                          cudaStream_t stream, bool pdl) {
+  launch(finalize_wide_kernel, dim3(sessions), dim3(512), 0, stream, pdl, best_value, best_index, parts,
+         rows_per_session, targets, step_tokens, slots);
 }
 
 void launch_accept(const uint32_t* inputs, const uint32_t* targets, int rows, int32_t* context_length,

@@ -265,8 +265,10 @@ def speculative_generate(session: Session, prompt: Sequence[int], drafts_for, ma
 
 
 class SessionBatch:
-    """Sessions of one model verified in one forward (weights streamed once for all of them); every session ends
-    exactly as after its own Session.verify. sessions * rows <= 16."""
+    """Sessions of one model verified in one forward (weights streamed once for all of them). Up to 16 stacked rows
+    (sessions * rows) every session ends exactly as after its own Session.verify, bit for bit; above that - up to
+    2048 stacked rows, 16 rows per session - the projections run on the tensor cores (the prompt GEMM) and the results
+    agree with the single-session step within the rounding of another summation order."""
 
     def __init__(self, sessions: Sequence["Session"]):
         self._lib = abi.load_library()

@@ -244,13 +244,17 @@ ei_status ei_session_verify(ei_session* session, const uint32_t* host_tokens, si
                             ei_verify_result* result, const void** logits);
 /* ---- several sessions in one forward --------------------------------------------------------------
  * No counterpart in the reference, whose sessions run one at a time. A batch is a fixed set of sessions of
- * one model (same device, same capacity, each listed once): ei_batch_verify stacks `rows` tokens of each
- * into one forward of sessions * rows <= 16 rows, so every weight is streamed once for all of them, while
+ * one model (same device, same capacity, each listed once; at most 1024): ei_batch_verify stacks `rows`
+ * (<= 16) tokens of each into one forward, so every weight is streamed once for all of them, while
  * attention, KV append, greedy acceptance and commit / rollback stay per session. host_tokens is
  * [sessions][rows] ([pending, d1..dk] of each session, in the order given to ei_batch_create), results is
- * [sessions]. Every session ends exactly as after its own ei_session_verify with the same tokens (same
- * bits). The step runs on the first session's stream and workspace; the other sessions must not be in use
- * from other threads during the call. Destroy the batch before its sessions. */
+ * [sessions]. Up to sessions * rows <= 16 stacked rows every session ends exactly as after its own
+ * ei_session_verify with the same tokens (same bits). Above that, up to 2048 stacked rows and for models
+ * whose projections the prompt GEMM takes, the forward runs on the tensor cores and one launch per kind of
+ * kernel serves all sessions; results then agree with the single-session step within the rounding of another
+ * summation order, and the sessions' logits buffers are not written. The step runs on the first session's
+ * stream (and workspace, or the model's prompt workspace); the other sessions must not be in use from other
+ * threads during the call. Destroy the batch before its sessions. */
 typedef struct ei_batch ei_batch;
 ei_status ei_batch_create(ei_session* const* sessions, size_t count, ei_batch** out);
 void ei_batch_destroy(ei_batch* batch);
