@@ -4,8 +4,9 @@
 // The path is bound by KV bytes, so each KV byte is fetched once: a block owns one KV head and
 // one chunk of the sequence, and serves every query row of every query head of that KV group
 // (rows * heads/kv_heads <= 112 stacked rows, one 16-row MMA tile per warp). K and V tiles of
-// 64 tokens go through shared memory with 16-byte asynchronous copies, double buffered, in a
-// swizzled layout that makes the fragment loads conflict-free. Scores, running maxima and sums
+// 64 tokens are brought into shared memory by TMA (one tiled copy each for K and V, issued by one thread,
+// completing on an mbarrier; a ring of three tiles per block, every wait bounded) in the 128-byte-swizzled
+// layout [half of the head][token][128 B], which makes the fragment loads conflict-free. Scores, running maxima and sums
 // stay in FP32; numerators are rounded to BF16 only as the A operand of the PV product while the
 // denominator adds the unrounded values - the staging of the reference kernel
 // (operators/src/cuda/kernels/flash_attn_prefill.cu:236-252). Chunks write (o, m, l) partials to
@@ -14,7 +15,9 @@
 // replayed while the context grows; blocks beyond the live length return immediately.
 #include "kernels.cuh"
 
+#include <algorithm>
 #include <cfloat>
+#include <stdexcept>
 
 namespace ei {
 namespace {
@@ -24,32 +27,19 @@ constexpr int kDim = 128;
 constexpr int kPartial = 132;      // floats per (split, row, head): 128 outputs, m, l, padding
 constexpr int kTileBytes = kTile * kDim * 2;
 
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
-  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-  const int bytes = valid ? 16 : 0;  // 0 source bytes zero-fills the destination
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(kPending));
-}
+constexpr int kStages = 3;                     // K/V tiles in flight per block
+constexpr int kStageBytes = 2 * kTileBytes;    // one K tile and one V tile
+constexpr size_t kAttentionShared = size_t(kStages) * kStageBytes + 1024 /* alignment */ + 64;
 
-// Byte offset of (token, 16-byte chunk) inside a tile: chunk index XOR (token & 7).
+struct AttentionShared {
+  uint64_t full[kStages];
+  int failed;
+};
+
+// Byte offset of (token, 16-byte chunk of the 256-byte head row) inside a staged tile: the two 128-byte halves
+// of the rows are stored one after the other, and inside a half the chunk index is XORed with (token & 7).
 __device__ __forceinline__ int tile_offset(int token, int chunk) {
-  return token * (kDim * 2) + ((chunk ^ (token & 7)) << 4);
-}
-
-__device__ __forceinline__ void load_tile(unsigned char* k_smem, unsigned char* v_smem, const bf16* k,
-                                          const bf16* v, int kv_stride, int first_token, int end_token) {
-  for (int i = threadIdx.x; i < kTile * 16; i += blockDim.x) {
-    const int token = i >> 4, chunk = i & 15;
-    const int absolute = first_token + token;
-    const bool valid = absolute < end_token;
-    const size_t src = size_t(valid ? absolute : first_token) * kv_stride + chunk * 8;
-    cp_async_16(k_smem + tile_offset(token, chunk), k + src, valid);
-    cp_async_16(v_smem + tile_offset(token, chunk), v + src, valid);
-  }
+  return (chunk >> 3) * (kTile * 128) + token * 128 + (((chunk & 7) ^ (token & 7)) << 4);
 }
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
@@ -60,31 +50,43 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                : "r"(address));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* smem_ptr) {
+  const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(address));
+}
+
 // kDirect = false: the verify step. Block (split, kv head) covers one chunk of the sequence for all <= 16 query
 // rows and writes (o, m, l) partials for the merge kernel.
 // kDirect = true: a prompt of many rows. Block (query block, kv head) covers 16 consecutive query rows over their
 // whole causal history and writes the normalised output itself; blocks with the longest histories start first.
 template <bool kDirect>
-__global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__(224) verify_attention_kernel(const __grid_constant__ AttentionParams p) {
+  extern __shared__ unsigned char attention_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(attention_smem_raw) + 1023) &
+                                                         ~uintptr_t(1023));
+  AttentionShared* sh = reinterpret_cast<AttentionShared*>(smem + size_t(kStages) * kStageBytes);
   // The context length was written by the previous step; the preceding kernel of this step only appends the
   // new rows [offset, offset + rows). A chunk that ends before them can start fetching at once.
   // Wide batch (split form only): grid slice z is a session with its own cache, context length, queries, scratch.
   const SessionSlot* owner = (!kDirect && p.slots) ? p.slots + blockIdx.z : nullptr;
   const int capacity = owner ? owner->capacity : p.capacity;
   const int first_offset = owner ? owner->control->context : (p.device_offset ? *p.device_offset : p.host_offset);
-  const int kv_head = blockIdx.y;
+  // The KV heads of one stretch of tokens are neighbours in the grid, so the blocks that read the same cache rows
+  // (one 256-byte piece each) run at about the same time.
+  const int kv_head = blockIdx.x;
   if (first_offset < 0 || first_offset + p.rows > capacity) {
     // The whole grid leaves: it still waits for its predecessor first, so that a successor never sees this
     // kernel complete before the kernels ahead of it have.
     grid_dependency_wait();
     return;
   }
-  const int first_row = kDirect ? (int(gridDim.x) - 1 - int(blockIdx.x)) * 16 : 0;
+  const int first_row = kDirect ? (int(gridDim.y) - 1 - int(blockIdx.y)) * 16 : 0;
   const int rows = kDirect ? min(16, p.rows - first_row) : p.rows;
   const int offset = first_offset + first_row;
   const int length = offset + rows;
-  const int split = kDirect ? 0 : blockIdx.x;
+  const int split = kDirect ? 0 : blockIdx.y;
   const int start = kDirect ? 0 : split * p.chunk;
   if (start >= length) return;  // other blocks of the grid wait
   const int end = kDirect ? length : min(start + p.chunk, length);
@@ -92,18 +94,33 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   const int stacked = rows * group;  // query rows served by this block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
 
-  unsigned char* k_smem[2] = {smem, smem + 2 * kTileBytes};
-  unsigned char* v_smem[2] = {smem + kTileBytes, smem + 3 * kTileBytes};
-  const size_t layer_offset = owner ? size_t(p.layer) * size_t(capacity) * p.kv_stride : 0;
-  const bf16* k_base = (owner ? owner->k_cache + layer_offset : p.k) + size_t(kv_head) * kDim;
-  const bf16* v_base = (owner ? owner->v_cache + layer_offset : p.v) + size_t(kv_head) * kDim;
+  const CUtensorMap* k_map = owner ? p.maps + 2 * blockIdx.z : &p.k_map;
+  const CUtensorMap* v_map = owner ? p.maps + 2 * blockIdx.z + 1 : &p.v_map;
+  const int layer = owner ? p.layer : 0;
   const bf16* q_base = p.q + (owner ? size_t(blockIdx.z) * p.rows * p.q_stride : 0);
   float* scratch = p.scratch + (owner ? size_t(blockIdx.z) * p.scratch_stride : 0);
+  const uint32_t wait_limit = p.wait_limit ? p.wait_limit : kTmaWaitLimit;
+  const int tiles = (end - start + kTile - 1) / kTile;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) mbarrier_init(&sh->full[s], 1);
+    sh->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // One thread requests a tile: the K and the V box of 64 tokens of this KV head, one stage of the ring.
+  auto request = [&](int tile) {
+    const int stage = tile % kStages;
+    unsigned char* base = smem + size_t(stage) * kStageBytes;
+    mbarrier_expect_tx(&sh->full[stage], uint32_t(kStageBytes) + (tile == 0 ? p.fault_tx : 0u));
+    tma_load_5d(base, k_map, 0, start + tile * kTile, 0, kv_head, layer, &sh->full[stage]);
+    tma_load_5d(base + kTileBytes, v_map, 0, start + tile * kTile, 0, kv_head, layer, &sh->full[stage]);
+  };
 
   const bool settled = end <= offset;  // no row of this chunk is written by the preceding kernel
   if (!settled) grid_dependency_wait();
-  load_tile(k_smem[0], v_smem[0], k_base, v_base, p.kv_stride, start, end);
-  cp_async_commit();
+  if (threadIdx.x == 0)
+    for (int tile = 0; tile < min(kStages, tiles); ++tile) request(tile);
   if (settled) grid_dependency_wait();  // the queries come from the preceding kernel
   // Only now: a kernel that triggers after its own wait lets its successor's prologue see everything up to the
   // kernel before this one as complete, which is what the early fetch above relies on.
@@ -136,32 +153,40 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
   for (int d = 0; d < 16; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
 
-  const int tiles = (end - start + kTile - 1) / kTile;
-  for (int tile = 0; tile < tiles; ++tile) {
-    const int buffer = tile & 1;
-    if (tile + 1 < tiles) {
-      load_tile(k_smem[buffer ^ 1], v_smem[buffer ^ 1], k_base, v_base, p.kv_stride, start + (tile + 1) * kTile,
-                end);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    const unsigned char* ks = k_smem[buffer];
-    const unsigned char* vs = v_smem[buffer];
+  int tile = 0;
+  bool gave_up = false;
+  for (; tile < tiles; ++tile) {
+    const int stage = tile % kStages;
+    if (!mbarrier_wait(&sh->full[stage], (tile / kStages) & 1, wait_limit)) sh->failed = 1;
+    unsigned char* ks = smem + size_t(stage) * kStageBytes;
+    unsigned char* vs = ks + kTileBytes;
     const int first = start + tile * kTile;
+    if (end - first < kTile) {
+      // The last tile reaches past the live rows: what the copy brought for them is whatever the cache holds
+      // there (rows of rejected drafts, or memory never written). Their scores are masked below; their V rows
+      // are cleared so that a non-finite leftover cannot reach the PV product through a zero weight.
+      const int live = end - first;
+      for (int i = threadIdx.x; i < (kTile - live) * 16; i += blockDim.x) {
+        const int token = live + (i >> 4), chunk = i & 15;
+        *reinterpret_cast<uint4*>(vs + tile_offset(token, chunk)) = make_uint4(0, 0, 0, 0);
+      }
+      __syncthreads();
+    }
 
+    // S = Q K^T: n-tile j covers tokens 8j..8j+7. One ldmatrix.x4 brings the K fragments of two k-steps (four
+    // 16-byte chunks of eight token rows: lane l addresses row l & 7 of chunk l >> 3); the eight accumulators take
+    // their k-steps in ascending order, interleaved so that consecutive MMAs do not depend on each other.
     float s[8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-      const int token = j * 8 + g;
+    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(ks + tile_offset(token, 2 * kk) + 4 * c);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(ks + tile_offset(token, 2 * kk + 1) + 4 * c);
-        mma_bf16_16816(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+    for (int pair = 0; pair < 4; ++pair) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, ks + tile_offset(j * 8 + (lane & 7), 4 * pair + (lane >> 3)));
+        mma_bf16_16816(s[j], qa[2 * pair][0], qa[2 * pair][1], qa[2 * pair][2], qa[2 * pair][3], b0, b1);
+        mma_bf16_16816(s[j], qa[2 * pair + 1][0], qa[2 * pair + 1][1], qa[2 * pair + 1][2], qa[2 * pair + 1][3], b2, b3);
       }
     }
     // Scale, mask (causal and beyond-the-end), running maximum.
@@ -221,7 +246,20 @@ __global__ void __launch_bounds__(224) verify_attention_kernel(const AttentionPa
         mma_bf16_16816(o[d + 1], pa[2 * t][0], pa[2 * t][1], pa[2 * t + 1][0], pa[2 * t + 1][1], b2, b3);
       }
     }
-    __syncthreads();  // the buffer is refilled two iterations from now
+    __syncthreads();  // every warp is done with this stage
+    gave_up = sh->failed != 0;  // written before the barrier by any thread whose wait ran out: block-uniform
+    if (gave_up) break;
+    if (threadIdx.x == 0 && tile + kStages < tiles) request(tile + kStages);
+  }
+  if (gave_up) {
+    // Copies still in flight write into this block's shared memory: wait for them (bounded) before leaving. The
+    // copy of tile 0 carries the test hook's unmet expectation when that is armed and is known not to complete.
+    if (threadIdx.x == 0) {
+      for (int t = max(tile, p.fault_tx ? 1 : 0); t < min(tile + kStages, tiles); ++t)
+        mbarrier_wait(&sh->full[t % kStages], (t / kStages) & 1, wait_limit);
+      if (p.status) atomicOr(p.status, 4);
+    }
+    return;
   }
 
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -361,28 +399,54 @@ void configure_attention_kernels() {
   EI_CUDA(cudaGetDevice(&device));
   if (configured_device == device) return;
   EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               4 * kTileBytes));
+                               int(kAttentionShared)));
   EI_CUDA(cudaFuncSetAttribute(verify_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               4 * kTileBytes));
+                               int(kAttentionShared)));
   configured_device = device;
 }
+
+// The parameters with the single session's tensor maps filled in (a wide batch brings its own).
+AttentionParams with_maps(const AttentionParams& p) {
+  AttentionParams q = p;
+  if (!q.slots) {
+    encode_kv_map(&q.k_map, q.k, size_t(q.capacity), size_t(q.kv_stride), q.kv_heads, 1, 0);
+    encode_kv_map(&q.v_map, q.v, size_t(q.capacity), size_t(q.kv_stride), q.kv_heads, 1, 0);
+  } else if (!q.maps) {
+    throw std::invalid_argument("A wide attention launch needs the sessions' tensor maps");
+  }
+  return q;
+}
 }  // namespace
+
+void encode_kv_map(CUtensorMap* map, const bf16* base, size_t tokens, size_t token_stride, int kv_heads, size_t layers,
+                   size_t layer_stride) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || token_stride % 8 || layer_stride % 8)
+    throw std::invalid_argument("K / V rows must be 16-byte aligned");
+  const cuuint64_t dims[5] = {64, cuuint64_t(tokens), 2, cuuint64_t(kv_heads), cuuint64_t(std::max<size_t>(1, layers))};
+  const cuuint64_t strides[4] = {cuuint64_t(token_stride) * 2, 128, 256,
+                                 cuuint64_t(layers > 1 ? layer_stride : token_stride * std::max<size_t>(1, tokens)) * 2};
+  const cuuint32_t box[5] = {64, cuuint32_t(kTile), 2, 1, 1};
+  encode_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+             "K / V cache");
+}
 
 void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
   const int group = p.heads / p.kv_heads;
   const int warps = (p.rows * group + 15) / 16;
   configure_attention_kernels();
-  const unsigned sessions = p.slots ? unsigned(p.sessions) : 1u;
-  launch(verify_attention_kernel<false>, dim3(p.max_splits, p.kv_heads, sessions), dim3(warps * 32),
-         size_t(4 * kTileBytes), stream, pdl, p);
-  launch(attention_merge_kernel, dim3(p.rows * p.heads, sessions), dim3(128), 0, stream, pdl, p);
+  const AttentionParams q = with_maps(p);
+  const unsigned sessions = q.slots ? unsigned(q.sessions) : 1u;
+  launch(verify_attention_kernel<false>, dim3(q.kv_heads, q.max_splits, sessions), dim3(warps * 32), kAttentionShared,
+         stream, pdl, q);
+  launch(attention_merge_kernel, dim3(q.rows * q.heads, sessions), dim3(128), 0, stream, pdl, q);
 }
 
 void launch_prompt_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
   const int group = p.heads / p.kv_heads;
   configure_attention_kernels();
-  launch(verify_attention_kernel<true>, dim3((p.rows + 15) / 16, p.kv_heads), dim3(group * 32),
-         size_t(4 * kTileBytes), stream, pdl, p);
+  const AttentionParams q = with_maps(p);
+  launch(verify_attention_kernel<true>, dim3(q.kv_heads, (q.rows + 15) / 16), dim3(group * 32), kAttentionShared,
+         stream, pdl, q);
 }
 
 }  // namespace ei

@@ -27,15 +27,14 @@
 // outputs again.
 #pragma once
 
-#include <cuda.h>
-
 #include "smallm_gemm.cuh"
+#include "tma.cuh"
 
 namespace ei {
 
 constexpr int kAwqMaxStages = 12;
 constexpr int kAwqSliceUnits = 16;            // 256-input units per K slice: one per warp
-constexpr uint32_t kAwqWaitLimit = 1u << 22;  // polls of ~100 ns before a wait gives up
+constexpr uint32_t kAwqWaitLimit = kTmaWaitLimit;  // polls of ~100 ns before a wait gives up
 
 struct AwqTensorMaps {
   CUtensorMap weights;  // u32 [units][N][32], box [units_box][8][32], 128-byte swizzle
@@ -56,64 +55,6 @@ struct AwqLaunch {
   uint32_t extra_tx;    // test hook: bytes added to what the first weight copy is expected to deliver, so that
                         // its barrier never completes and the bounded waits run out (0 in production)
 };
-
-__device__ __forceinline__ uint32_t smem_address(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbarrier_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbarrier_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbarrier_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 100;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_address(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbarrier_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_address(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Bounded wait; false if the phase did not complete within the limit. The non-blocking test comes first: a
-// try_wait with a time hint costs a few hundred cycles even when the phase has long completed, which is the
-// normal case here (the ring runs ahead of the arithmetic).
-__device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kAwqWaitLimit) {
-  if (mbarrier_test_wait(bar, parity)) return true;
-  for (uint32_t polls = 0; polls < limit; ++polls)
-    if (mbarrier_try_wait(bar, parity)) return true;
-  return false;
-}
-// Tiled TMA loads; coordinates run from the innermost dimension outwards. x times the element size must be
-// a multiple of 16 bytes (the callers below only pass multiples of whole slices).
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
-          "r"(smem_address(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_address(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], "
-      "[%5];" ::"r"(smem_address(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_address(bar))
-      : "memory");
-}
 
 constexpr int kAwqPhaseTiles = 2;  // tiles a warp accumulates between two block-wide barriers
 constexpr int kAwqEarlyPhases = 1; // phases (pairs of tiles) requested before the kernel waits for its predecessor

@@ -2,6 +2,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ei {
 
@@ -121,7 +122,20 @@ struct AttentionParams {
   const SessionSlot* slots; // wide batch: one grid slice per session (`sessions` of them), `rows` query rows
   int sessions, layer;      // each; session j reads q + j * rows * q_stride, its own cache and context length,
   size_t scratch_stride;    // scratch + j * scratch_stride (floats), and writes out + j * rows * out_stride
+  // K / V tiles are fetched by TMA. A single session's maps are encoded by the launch function from k, v,
+  // kv_stride, kv_heads and capacity; a wide batch passes one pair per session in device memory, built with
+  // encode_kv_map over all layers of the session's cache (`layer` selects the slice).
+  CUtensorMap k_map, v_map;
+  const CUtensorMap* maps;  // [sessions][2] = (K, V)
+  int* status;              // optional device word; bit 2 is set if a bounded wait on a copy gave up
+  uint32_t wait_limit;      // polls before a bounded wait gives up (0: the default)
+  uint32_t fault_tx;        // test hook: bytes the first copy is expected to deliver beyond what it does (0 in production)
 };
+// Tensor map of a K or V cache: bf16 [layers][tokens][kv_heads * 128] with `token_stride` elements between tokens
+// and `layer_stride` between layers, described to TMA as (64 values, token, half of a head, kv head, layer) so
+// that a 64-token tile of one head lands as [half][token][128 B] with the 128-byte swizzle.
+void encode_kv_map(CUtensorMap* map, const bf16* base, size_t tokens, size_t token_stride, int kv_heads, size_t layers,
+                   size_t layer_stride);
 int attention_chunk_for(size_t kv_length);
 size_t attention_scratch_bytes(size_t rows, size_t heads, size_t kv_length);
 void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);

@@ -325,7 +325,4 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
   if (threadIdx.x == 0 && sh->abort && p.status) atomicOr(p.status, 4);
 }
 
-void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
-                const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle, const char* what);
-
 }  // namespace ei

@@ -335,6 +335,7 @@ struct ei_batch {
   // Wide form (more than 16 stacked rows): the sessions' slots on the device, and buffers sized on first use
   // for sessions * rows stacked rows.
   SessionSlot* slots = nullptr;
+  CUtensorMap* maps = nullptr;      // [sessions][2]: TMA descriptions of every session's K and V cache, all layers
   unsigned char* wide_arena = nullptr;
   size_t wide_rows = 0;
   bf16* logits = nullptr;           // [stacked rows, vocab]
@@ -691,6 +692,7 @@ void enqueue_prompt_segment(ei_session& s, int rows, bool head) {
     a.kv_heads = kv_heads;
     a.capacity = int(s.capacity);
     a.device_offset = &s.control->context;
+    a.status = &s.control->status;
     a.out = ws.attention;
     a.out_stride = heads * 128;
     tick(s);
@@ -790,6 +792,7 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
     a.kv_heads = kv_heads;
     a.capacity = int(s.capacity);
     a.device_offset = &s.control->context;
+    a.status = &s.control->status;
     a.chunk = s.attention_chunk;
     a.max_splits = s.attention_splits;
     a.scratch = s.attention_scratch;
@@ -946,6 +949,7 @@ void enqueue_batch_step(ei_batch& batch, int rows) {
       a.kv_heads = kv_heads;
       a.capacity = int(s.capacity);
       a.device_offset = &s.control->context;
+      a.status = &s.control->status;
       a.chunk = s.attention_chunk;
       a.max_splits = s.attention_splits;
       a.scratch = lead.attention_scratch + size_t(j) * scratch_floats;
@@ -1090,6 +1094,8 @@ void enqueue_wide_batch_step(ei_batch& batch, int rows) {
     a.out = ws.attention;
     a.out_stride = heads * 128;
     a.slots = batch.slots;
+    a.maps = batch.maps;
+    a.status = &lead.control->status;
     a.sessions = count;
     a.layer = int(layer);
     tick(lead);
@@ -1523,10 +1529,21 @@ ei_status ei_batch_create(ei_session* const* sessions, size_t count, ei_batch** 
     std::vector<SessionSlot> slots(count);
     for (size_t j = 0; j < count; ++j)
       slots[j] = SessionSlot{sessions[j]->control, sessions[j]->k_cache, sessions[j]->v_cache, int(sessions[j]->capacity), 0};
+    const auto& c = sessions[0]->model->config;
+    const size_t kv_width = c.n_kv_heads * 128;
+    std::vector<CUtensorMap> maps(2 * count);
+    for (size_t j = 0; j < count; ++j) {
+      const ei_session& s = *sessions[j];
+      encode_kv_map(&maps[2 * j], s.k_cache, s.capacity, kv_width, int(c.n_kv_heads), c.n_layers, s.capacity * kv_width);
+      encode_kv_map(&maps[2 * j + 1], s.v_cache, s.capacity, kv_width, int(c.n_kv_heads), c.n_layers, s.capacity * kv_width);
+    }
     EI_CUDA(cudaMalloc(reinterpret_cast<void**>(&batch->slots), count * sizeof(SessionSlot)));
-    if (cudaMemcpy(batch->slots, slots.data(), count * sizeof(SessionSlot), cudaMemcpyHostToDevice) != cudaSuccess ||
+    if (cudaMalloc(reinterpret_cast<void**>(&batch->maps), maps.size() * sizeof(CUtensorMap)) != cudaSuccess ||
+        cudaMemcpy(batch->maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(batch->slots, slots.data(), count * sizeof(SessionSlot), cudaMemcpyHostToDevice) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void**>(&batch->host_controls), count * sizeof(Control)) != cudaSuccess) {
       cudaFree(batch->slots);
+      if (batch->maps) cudaFree(batch->maps);
       throw std::runtime_error("Batch state could not be placed on the device");
     }
     *out = batch.release();
@@ -1539,6 +1556,7 @@ void ei_batch_destroy(ei_batch* batch) {
     if (exec) cudaGraphExecDestroy(exec);
   if (!batch->sessions.empty()) cudaStreamSynchronize(batch->sessions[0]->stream);
   if (batch->slots) cudaFree(batch->slots);
+  if (batch->maps) cudaFree(batch->maps);
   if (batch->wide_arena) cudaFree(batch->wide_arena);
   if (batch->host_controls) cudaFreeHost(batch->host_controls);
   delete batch;

@@ -150,7 +150,7 @@ EncodeTiled tensor_map_encoder() {
 
 void encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
                 const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle, const char* what) {
-  const cuuint32_t ones[3] = {1, 1, 1};
+  const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
   const CUresult result = tensor_map_encoder()(map, type, cuuint32_t(rank), const_cast<void*>(base), dims, strides, box,
                                                ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
