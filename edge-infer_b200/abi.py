@@ -153,6 +153,7 @@ PROTOTYPES = {
     "ei_session_adopt_history": (_S, [_P, C.c_size_t, C.c_uint32]),
     "ei_session_inject_failure": (_S, [_P, C.c_int, C.c_int]),
     "ei_session_inject_wait_timeout": (_S, [_P, C.c_uint32]),
+    "ei_session_inject_attention_wait_timeout": (_S, [_P, C.c_uint32]),
 }
 
 _lib = None

@@ -318,6 +318,7 @@ struct ei_session {
   size_t bound = 0;  // upper bound of the context length after every step enqueued so far (full acceptance)
   bool history_ready = false, poisoned = false;
   int inject_launch = 0, inject_completion = 0;
+  uint32_t inject_attention_polls = 0;  // the same hook for the next attention launch (its K / V tile copies)
   uint32_t inject_wait_polls = 0;  // test hook: the next weight-streaming GEMM gets this poll limit and a copy
                                    // expectation it cannot meet, so that its bounded waits run out
   size_t launches = 0, launches_per_step[kMaxRows + 1] = {};
@@ -798,6 +799,11 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
     a.scratch = s.attention_scratch;
     a.out = s.attention;
     a.out_stride = heads * 128;
+    if (s.inject_attention_polls) {
+      a.wait_limit = s.inject_attention_polls;
+      a.fault_tx = 16;
+      s.inject_attention_polls = 0;  // one launch only
+    }
     tick(s);
     tick(s);
     launch_verify_attention(a, s.stream, pdl);
@@ -849,7 +855,7 @@ void enqueue_step(ei_session& s, int rows, StepKind kind, bf16* logits_out) {
 
 // Runs a step either eagerly or by replaying its graph (captured on first use after an eager warm run).
 void submit_step(ei_session& s, int rows, StepKind kind) {
-  if (!s.use_graph || kind == kCommitAllNoHead || s.inject_wait_polls) {
+  if (!s.use_graph || kind == kCommitAllNoHead || s.inject_wait_polls || s.inject_attention_polls) {
     enqueue_step(s, rows, kind, nullptr);
     return;
   }
@@ -2014,6 +2020,13 @@ ei_status ei_session_inject_wait_timeout(ei_session* session, uint32_t polls) {
   return guarded([&] {
     if (!session || !polls) throw std::invalid_argument("session is null or the poll limit is zero");
     session->inject_wait_polls = polls;
+  });
+}
+
+ei_status ei_session_inject_attention_wait_timeout(ei_session* session, uint32_t polls) {
+  return guarded([&] {
+    if (!session || !polls) throw std::invalid_argument("session is null or polls is zero");
+    session->inject_attention_polls = polls;
   });
 }
 

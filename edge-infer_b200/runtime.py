@@ -212,6 +212,10 @@ class Session:
         """Test hook: the next weight-streaming GEMM's bounded waits run out after `polls` polls."""
         abi.check(self._lib.ei_session_inject_wait_timeout(self._handle, polls))
 
+    def inject_attention_wait_timeout(self, polls: int) -> None:
+        """Test hook: the bounded waits of the next attention launch (its K / V tile copies) run out after `polls`."""
+        abi.check(self._lib.ei_session_inject_attention_wait_timeout(self._handle, polls))
+
     def close(self) -> None:
         if self._handle:
             self._lib.ei_session_destroy(self._handle)

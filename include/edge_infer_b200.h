@@ -342,6 +342,9 @@ ei_status ei_session_inject_failure(ei_session* session, int nth_launch, int com
  * own stream is drained and its history forgotten (prefill again); other sessions are untouched.
  * ref: the drain-or-poison rules of runtime/src/qwen3.cpp:127-161. No counterpart in the reference's API. */
 ei_status ei_session_inject_wait_timeout(ei_session* session, uint32_t polls);
+/* The same hook for the attention kernel: the first K / V tile copy of every block of this session's next
+ * attention launch is told to expect 16 bytes more than it delivers. No counterpart in the reference's API. */
+ei_status ei_session_inject_attention_wait_timeout(ei_session* session, uint32_t polls);
 
 #ifdef __cplusplus
 }

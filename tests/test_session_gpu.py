@@ -391,6 +391,30 @@ def test_bounded_device_wait_runs_out_and_is_reported(cuda, package):
         assert np.array_equal(sibling.read_logits(1), sibling_logits)
 
 
+def test_bounded_wait_in_the_attention_kernel_runs_out_and_is_reported(cuda, package):
+    """The same for the attention kernel's K / V tile copies (TMA on an mbarrier ring): every block of one launch
+    gives up after 2000 polls, waits for its other copies in flight, raises the status bit and returns."""
+    syn, abi = package.synthetic, package.abi
+    shape = shapes(package)["qwen3_awq"]
+    model = package.Model(shape, syn.make_model(shape, seed=1))
+    session = model.new_session(256, graph=True)
+    prompt = syn.make_prompt(2, 150, shape.vocab_size)
+    session.prefill(prompt)
+    expected = session.read_logits(1).copy()
+    first = session.verify([7, 8, 9])
+    session.truncate(150)
+    session.inject_attention_wait_timeout(2000)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        session.verify([7, 8, 9])
+    assert session.context_size() == 0
+    with pytest.raises(abi.LogicError):
+        session.verify([7, 8, 9])
+    session.prefill(prompt)
+    assert np.array_equal(session.read_logits(1), expected)
+    again = session.verify([7, 8, 9])
+    assert again.targets == first.targets and again.emitted == first.emitted
+
+
 def test_enqueue_refuses_steps_that_could_pass_the_capacity(cuda, package):
     """Between drains the host bounds the context length by full acceptance: a chained step that could pass the
     capacity is refused before anything is submitted, the history stays, and the chain continues after a drain."""
