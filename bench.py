@@ -382,7 +382,7 @@ def prompt_leg(shape, ms: float) -> dict:
                     "tcgen05 (int4 dequantised in shared memory), one attention launch over all rows"}
 
 
-def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int):
+def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int, profile: bool = False):
     """The sharded-sessions configuration: 64 sessions of the Qwen2.5-7B-shaped AWQ model with seeded prompt lengths
     in [256, 8192], split evenly over the ranks, k = 4 drafts with p = 0.3 substitution. Every forward verifies ALL
     sessions of the rank at once (ei_batch_verify in its wide form: the stacked rows go through the projections as
@@ -461,6 +461,15 @@ def run_sessions_leg(package, torch, dist, rank: int, world: int, rounds: int):
             dist.barrier()
         return emitted, elapsed_ms
 
+    if profile:                                                # for `ncu --profile-from-start off`: one forward of all sessions
+        rewind()
+        run(1, [list(range(len(sessions)))], [everyone])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        run(1, [list(range(len(sessions)))], [everyone])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return {"profiled": "one forward of all %d sessions" % len(sessions)}
     kv_per_token = 2 * shape.n_layers * kv_width * 2
     narrow_rounds = max(2, rounds // 6)
     narrow_emitted, narrow_ms = timed(narrow_rounds, batches, groups)
@@ -509,6 +518,13 @@ def run_native(args, rank: int, world: int, local_rank: int):
     package = entry.load_package()
     package.abi.load_library()
     syn = package.synthetic
+    if args.profile_sessions:
+        leg = run_sessions_leg(package, torch, dist, rank, world, rounds=2, profile=True)
+        if rank == 0:
+            print(json.dumps(leg))
+        if dist:
+            dist.destroy_process_group()
+        return
     shape = syn.qwen3_8b_awq(max_position_embeddings=CAPACITY)
     rows = K_DRAFTS + 1
 
@@ -746,6 +762,8 @@ def main():
     parser.add_argument("--profile-region", action="store_true",
                         help="bracket the timed steps with cudaProfilerStart/Stop (for a profiler started with "
                              "profiling off); the numbers of such a run are not bench values")
+    parser.add_argument("--profile-sessions", action="store_true",
+                        help="run only the 64-session leg and bracket one forward of all sessions the same way")
     parser.add_argument("--profile-prompt", action="store_true",
                         help="bracket one prefill of the prompt the same way and stop after it")
     args = parser.parse_args()
