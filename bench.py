@@ -362,6 +362,47 @@ def time_reference_cuda(package, oracle, torch, shape, tensors, drafts, first, s
     return seconds / steps, emitted / steps, prompt_seconds
 
 
+def run_speculative_leg(package, torch, target_model, rounds: int) -> dict:
+    """Whole speculative rounds (the reference's SpeculativeDecoder loop, runtime/src/speculative_decoder.cpp:227-306)
+    with the 8B-shape AWQ target and a 0.6B-shape BF16 draft, k = 8: nine draft decode steps chained on the device,
+    one verify forward, the hand-over between the two sessions; the host synchronises once for all rounds. Both models
+    are random-init, so nearly every draft is rejected: the figure is the time of a round and its parts, not the
+    acceptance."""
+    syn = package.synthetic
+    draft_shape = syn.qwen3_0_6b(max_position_embeddings=CAPACITY)
+    draft_model = package.Model(draft_shape, syn.make_device_model(draft_shape, seed=1))
+    target, draft = target_model.new_session(CAPACITY, graph=True), draft_model.new_session(CAPACITY, graph=True)
+    decoder = package.runtime.SpeculativeDecoder(target, draft, K_DRAFTS)
+    prompt = syn.make_prompt(SEED, PROMPT, target_model.shape.vocab_size)
+    decoder.prefill(prompt)
+    decoder.enqueue(3)
+    decoder.drain()
+    decoder.truncate(1)
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    decoder.enqueue(rounds)
+    produced = decoder.drain()
+    round_ms = (time.perf_counter() - begin) * 1e3 / rounds
+    # One draft decode step alone, chained the same way (no host synchronisation between steps).
+    decoder.close()
+    draft.prefill(prompt)
+    token = 1
+    draft.decode(token)
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    for _ in range(32):
+        draft.decode(token)
+    torch.cuda.synchronize()
+    draft_ms = (time.perf_counter() - begin) * 1e3 / 32
+    del target, draft, draft_model
+    torch.cuda.empty_cache()
+    return {"workload": "qwen3-8b-shape AWQ target + qwen3-0.6b-shape BF16 draft, k=8, prompt 2048, rounds chained on "
+                        "the device, one host synchronisation for all rounds",
+            "rounds": rounds, "ms_per_round": round_ms, "tokens_per_round": (len(produced) - 1) / rounds,
+            "draft_decode_ms_per_token_host_driven": draft_ms,
+            "note": "random-init draft: nearly every draft is rejected, so tokens_per_round is about 1"}
+
+
 def prompt_leg(shape, ms: float) -> dict:
     """Prefill of the benchmark's 2048-token prompt through the public call. The arithmetic counted is the four
     projections of every layer over all rows (2 * rows * N * K each) and causal attention (QK and PV over half the
@@ -725,6 +766,8 @@ def run_native(args, rank: int, world: int, local_rank: int):
             else:
                 line["reference_cuda"] = {"unavailable": "oracle/_ref is not built"}
     keep_tensors = None
+    if rank == 0 and not args.no_sessions_leg:
+        line["speculative_leg"] = run_speculative_leg(package, torch, model, rounds=24)
     del model
     torch.cuda.empty_cache()
     if not args.no_sessions_leg:

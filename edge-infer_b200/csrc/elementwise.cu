@@ -8,6 +8,7 @@
 // the four products and both sums (operators/src/cuda/execution.cu:104-117); the residual
 // add is one rounded FP32 sum of two BF16 values (operators/src/cuda/add_cuda.cu:42-62).
 #include "kernels.cuh"
+#include "head_math.cuh"
 #include "smallm_gemm.cuh"
 
 namespace ei {
@@ -26,11 +27,6 @@ __device__ __forceinline__ float block_sum(float v, float* shared) {
   const float total = warp_sum(shared[lane]);
   __syncthreads();
   return total;
-}
-
-// 1 / sqrt(mean + eps) as the reference computes it (its build divides with the fast reciprocal-multiply).
-__device__ __forceinline__ float inverse_rms(float sum_of_squares, int width, float eps) {
-  return rsqrtf(__fdividef(sum_of_squares, float(width)) + eps);
 }
 
 __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const bf16* in, const bf16* weight,
@@ -88,14 +84,6 @@ __global__ void gather_rows_kernel(const uint32_t* ids, const bf16* table, bf16*
     const uint32_t token = ids[row];
     out[at] = token < vocabulary ? table[size_t(token) * width + column] : __float2bfloat16_rn(0.0f);
   }
-}
-
-__device__ __forceinline__ void rotate_pair(float x, float y, float sine, float cosine, float& first,
-                                            float& second) {
-  sine = round_bf16(sine);
-  cosine = round_bf16(cosine);
-  first = round_bf16(round_bf16(x * cosine) - round_bf16(y * sine));
-  second = round_bf16(round_bf16(x * sine) + round_bf16(y * cosine));
 }
 
 // Half-split RoPE in place over [rows, heads, width]: a thread owns rotation pair `pair` of one head row,
@@ -186,25 +174,6 @@ __global__ void __launch_bounds__(kNormThreads) embed_norm_kernel(const EmbedPar
     if (i < p.hidden)
       normed[i] = __float2bfloat16_rn(round_bf16(values[j] * inv) * __bfloat162float(p.norm_weight[i]));
   }
-}
-
-// Inverse RMS of a 128-wide head row with the sum of squares in the order of the reference's norm kernel
-// (operators/src/cuda/rms_norm_cuda.cu:27-72 run over [rows * heads, 128]: one element per thread, a shuffle tree
-// over each block of 32 elements - offsets 16, 8, 4, 2, 1 - and the four block sums combined as
-// (p0 + p2) + (p1 + p3)), so that it has the reference's bits. Lane l of the warp holds elements 2l, 2l+1
-// (x0, x1) and 64+2l, 64+2l+1 (y0, y1).
-__device__ __forceinline__ float head_inverse_rms(float x0, float x1, float y0, float y1, float eps) {
-  float a = x0 * x0, b = x1 * x1, a2 = y0 * y0, b2 = y1 * y1;
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) {  // element offsets 16, 8, 4, 2 inside a block of 32 elements = 16 lanes
-    a += __shfl_xor_sync(0xffffffffu, a, o);
-    b += __shfl_xor_sync(0xffffffffu, b, o);
-    a2 += __shfl_xor_sync(0xffffffffu, a2, o);
-    b2 += __shfl_xor_sync(0xffffffffu, b2, o);
-  }
-  const float q = (a + b) + (a2 + b2);  // lanes 0-15: p0 + p2, lanes 16-31: p1 + p3
-  const float total = q + __shfl_xor_sync(0xffffffffu, q, 16);
-  return rsqrtf(__fdividef(total, 128.0f) + eps);
 }
 
 // One warp per (row, head); lane l owns rotation pairs 2l and 2l+1, i.e. elements
