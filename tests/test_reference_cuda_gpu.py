@@ -17,8 +17,10 @@ max|ref| of the step):
   * a minimum number of decisive rows (reference top-2 gap above twice the element bound) per run, every one of
     which must give the reference's greedy token, and the reference's accept length whenever the emitted prefix is
     decisive.
-Every run also appends its measured figures to gpurun_out/reference_parity.jsonl when that folder exists."""
+Every run also appends its measured figures, one JSON line each, to the file the environment variable
+EDGE_INFER_PARITY_RECORD names (when it is set)."""
 import json
+import os
 from pathlib import Path
 
 import numpy as np
@@ -154,9 +156,9 @@ def run_against_reference(torch, package, oracle, name, shape, tensors_for_libra
     record.update(decisive_rows=decisive_rows, token_mismatches=int(token_mismatches), accept_checked=accept_checked,
                   accept_mismatches=int(accept_mismatches), rows_total=rows_total, rows_equal=int(rows_equal),
                   rms_max=max(s["rms"] for s in record["steps"]), max_max=max(s["max"] for s in record["steps"]))
-    out_dir = ROOT / "gpurun_out"
-    if out_dir.is_dir():
-        with open(out_dir / "reference_parity.jsonl", "a") as handle:
+    record_path = os.environ.get("EDGE_INFER_PARITY_RECORD")
+    if record_path:
+        with open(record_path, "a") as handle:
             handle.write(json.dumps(record) + "\n")
     assert token_mismatches == 0 and accept_mismatches == 0, record
     assert decisive_rows >= minimum, record
