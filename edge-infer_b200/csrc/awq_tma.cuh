@@ -218,12 +218,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   bool sz_ok = true;
   if (kTmaSz) sz_ok = mbarrier_wait(sz_full, 0, wait_limit);
 
+  // With at most eight rows the operands trade places: the two tiles of a phase (16 features) are the A operand of
+  // one MMA and the rows the B operand, so an MMA covers 256 weights instead of 128 and a phase has one accumulator
+  // fragment (features x rows) instead of two (rows x features, half of them empty).
+  constexpr bool kSwap = !kHigh;
   // Reduction role of this lane: warp r owns accumulator elements e in [8r, 8r + 8); a lane is (part, element).
   const int e = warp * 8 + (lane & 7);
   const int part_index = lane >> 3;
   const int rl = e >> 2, reg = e & 3;
-  const int row = (rl >> 2) + (reg >= 2 ? 8 : 0);
-  const int col = (rl & 3) * 2 + (reg & 1);
+  // Element (lane rl, register reg) of a fragment: (row, col) of the output it belongs to, and for the swapped
+  // form the tile of the phase (`swap_tile`): there the fragment's rows are features and its columns output rows.
+  const int row = kSwap ? (rl & 3) * 2 + (reg & 1) : (rl >> 2) + (reg >= 2 ? 8 : 0);
+  const int col = kSwap ? (rl >> 2) : (rl & 3) * 2 + (reg & 1);
+  const int swap_tile = reg >> 1;
   const int unit_group = warp * 2;  // the unit's two scale groups within the slice: cells 0-3 and cells 4-7
   // Everything a tile's addresses depend on is folded into per-lane constants here, so that the loop does no
   // division and little integer arithmetic (the loop is issue-bound: every instruction in it counts).
@@ -295,6 +302,68 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     acc[0] += other[0]; acc[1] += other[1]; acc[2] += other[2]; acc[3] += other[3];
   };
 
+  // Swapped form: both tiles of the phase at once. Lane (g, c) dequantises its word of row g of either tile; the
+  // A operand takes (tile 0 row g, tile 1 row g) as rows g and g + 8, the B operand the activation fragments.
+  auto compute_phase = [&](uint32_t tile_address, int step, bool second, float (&acc)[4]) {
+    float other[4];
+    if (!live) {
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+      return;
+    }
+    uint32_t scale2[2][2], zero2[2][2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      if (kTmaSz) {
+        const int sz_row = step * phase_rows + t * second_rows;
+        const uint32_t zero_word = shared_u32(lane_zero + sz_row * zero_pitch);
+        const uint32_t scales = shared_u32(lane_scale + sz_row * scale_pitch);
+        scale2[t][0] = (scales & 0xffffu) * 0x10001u;
+        scale2[t][1] = (scales >> 16) * 0x10001u;
+        zero2[t][0] = (0x4300u | ((zero_word >> zero_shift) & 15u)) * 0x10001u;
+        zero2[t][1] = (0x4300u | ((zero_word >> (zero_shift + 4)) & 15u)) * 0x10001u;
+      } else {
+        const uint32_t offset = uint32_t(step * kAwqPhaseTiles + t) * layout.sz_tile_bytes;
+        const uint32_t scales = shared_u32(lane_scale + offset);
+        uint32_t nibbles;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(nibbles) : "r"(lane_zero + offset));
+        scale2[t][0] = (scales & 0xffffu) * 0x10001u;
+        scale2[t][1] = (scales >> 16) * 0x10001u;
+        zero2[t][0] = (0x4300u | (nibbles & 15u)) * 0x10001u;
+        zero2[t][1] = (0x4300u | ((nibbles >> 8) & 15u)) * 0x10001u;
+      }
+    }
+    uint32_t words[2][8];
+#pragma unroll
+    for (int cell = 0; cell < 8; ++cell) {
+      words[0][cell] = shared_u32((tile_address + lane_word) ^ uint32_t(cell << 4));
+      // A phase without a second tile (the last one of an odd count) feeds zeros: its half of the fragment is
+      // never emitted, and zeros keep the arithmetic finite.
+      words[1][cell] = second ? shared_u32((tile_address + uint32_t(layout.weight_bytes) + lane_word) ^ uint32_t(cell << 4))
+                              : 0u;
+    }
+#pragma unroll
+    for (int cell = 0; cell < 8; ++cell) {
+      const int half = cell >> 2;
+      const uint32_t w0 = words[0][cell], w1 = words[1][cell];
+      const uint32_t a0 = dequant_pair(w0, zero2[0][half], scale2[0][half]);
+      const uint32_t a1 = dequant_pair(w1, zero2[1][half], scale2[1][half]);
+      const uint32_t a2 = dequant_pair(w0 >> 4, zero2[0][half], scale2[0][half]);
+      const uint32_t a3 = dequant_pair(w1 >> 4, zero2[1][half], scale2[1][half]);
+      const uint32_t c0 = dequant_pair(w0 >> 8, zero2[0][half], scale2[0][half]);
+      const uint32_t c1 = dequant_pair(w1 >> 8, zero2[1][half], scale2[1][half]);
+      const uint32_t c2 = dequant_pair(w0 >> 12, zero2[0][half], scale2[0][half]);
+      const uint32_t c3 = dequant_pair(w1 >> 12, zero2[1][half], scale2[1][half]);
+      if (cell == 0) {
+        mma_bf16_16816_first(acc, a0, a1, a2, a3, frag[cell].a[0][0], frag[cell].a[0][1]);
+        mma_bf16_16816_first(other, c0, c1, c2, c3, frag[cell].a[1][0], frag[cell].a[1][1]);
+      } else {
+        mma_bf16_16816(acc, a0, a1, a2, a3, frag[cell].a[0][0], frag[cell].a[0][1]);
+        mma_bf16_16816(other, c0, c1, c2, c3, frag[cell].a[1][0], frag[cell].a[1][1]);
+      }
+    }
+    acc[0] += other[0]; acc[1] += other[1]; acc[2] += other[2]; acc[3] += other[3];
+  };
+
   // Reduction of one phase (kAwqPhaseTiles tiles): the partials were read into `loaded` right after the
   // phase's barrier; the additions happen one tile of computation later, so the shared-memory latency is
   // hidden behind that tile's arithmetic. After the shuffles all four parts of a warp hold the same sums:
@@ -303,6 +372,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   float held[kAwqPhaseTiles] = {0.0f, 0.0f};
   auto emit = [&](int first_step, int last_step) {  // epilogue of phases first_step + part_index <= last_step
     const int step = first_step + part_index;
+    if (kSwap) {
+      // held[0] is this lane's element of the phase's single fragment: feature `col` of tile `swap_tile`, row `row`.
+      // In pair mode the gate value sits in registers 0-1 and its up value two registers on: two lanes further.
+      const float partner = __shfl_down_sync(0xffffffffu, held[0], 2);
+      if (step > last_step || row >= p.M) return;
+      const int index = step * kAwqPhaseTiles;
+      if (pair) {
+        if (swap_tile) return;
+        const int out_n = tile_of(item_begin + index) * 8 + col;
+        float gate = held[0], up = partner;
+        if (p.bias) {
+          gate += __bfloat162float(p.bias[out_n]);
+          up += __bfloat162float(p.bias[out_n + p.N / 2]);
+        }
+        p.out[size_t(row) * p.out_stride + out_n] =
+            __float2bfloat16_rn(silu_multiply_value(round_bf16(gate), round_bf16(up)));
+        return;
+      }
+      if (index + swap_tile >= item_count) return;
+      const int n = tile_of(item_begin + index + swap_tile) * 8 + col;
+      float sum = held[0];
+      if (p.epilogue == kEpiPartial) {
+        p.partial[(size_t(slice) * p.M + row) * p.N + n] = sum;
+      } else {
+        if (p.bias) sum += __bfloat162float(p.bias[n]);
+        p.out[size_t(row) * p.out_stride + n] = __float2bfloat16_rn(sum);
+      }
+      return;
+    }
     if (step > last_step || row >= p.M) return;
     const int index = step * kAwqPhaseTiles;
     if (pair) {
@@ -332,7 +430,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   };
   auto finish = [&](int step, const float (&loaded)[kAwqPhaseTiles][4]) {
 #pragma unroll
-    for (int t = 0; t < kAwqPhaseTiles; ++t) {
+    for (int t = 0; t < (kSwap ? 1 : kAwqPhaseTiles); ++t) {
       float sum = 0.0f;
 #pragma unroll
       for (int w = 0; w < 4; ++w) sum += loaded[t][w];
@@ -353,14 +451,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   for (int index = 0, step = 0; index < item_count && !gave_up; index += kAwqPhaseTiles, ++step) {
     const int phase = step & 1;
     float acc[kAwqPhaseTiles][4];
-    const bool ok = sz_ok && mbarrier_wait(&full[slot], parity, wait_limit);
+    // Warp-uniform: the shuffles of the reduction below are taken by whole warps or not at all.
+    const bool ok = __all_sync(0xffffffffu, sz_ok && mbarrier_wait(&full[slot], parity, wait_limit));
     const uint32_t tile_address = stages_address + uint32_t(slot) * uint32_t(phase_bytes);
-    if (ok) compute_tile(tile_address, step, 0, acc[0]);
-    if (ok && pending >= 0) finish(pending, loaded);
-    if (ok && (kPair || index + 1 < item_count))  // pairs come whole
-      compute_tile(tile_address + layout.weight_bytes, step, 1, acc[1]);
-    else
-      acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
+    if (kSwap) {
+      if (ok) compute_phase(tile_address, step, kPair || index + 1 < item_count, acc[0]);
+      if (ok && pending >= 0) finish(pending, loaded);
+    } else {
+      if (ok) compute_tile(tile_address, step, 0, acc[0]);
+      if (ok && pending >= 0) finish(pending, loaded);
+      if (ok && (kPair || index + 1 < item_count))  // pairs come whole
+        compute_tile(tile_address + layout.weight_bytes, step, 1, acc[1]);
+      else
+        acc[1][0] = acc[1][1] = acc[1][2] = acc[1][3] = 0.0f;
+    }
     if (++slot == ring_phases) {
       slot = 0;
       parity ^= 1;
@@ -368,7 +472,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     float* mine = part + (size_t(phase) * kAwqPhaseTiles * kGemmWarps + warp) * kBlock + lane * 4;
     if (ok) {
 #pragma unroll
-      for (int t = 0; t < kAwqPhaseTiles; ++t)
+      for (int t = 0; t < (kSwap ? 1 : kAwqPhaseTiles); ++t)
         *reinterpret_cast<float4*>(mine + size_t(t) * kGemmWarps * kBlock) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
     }
     // The decision to give up is the block's: a thread whose wait ran out raises the flag before the phase's
@@ -379,7 +483,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // Every warp has finished reading these stages: refill them with the tiles `stages` ahead.
     if (threadIdx.x == 0) issue(step + ring_phases);  // lands in the slot this phase has just left
 #pragma unroll
-    for (int t = 0; t < kAwqPhaseTiles; ++t) {
+    for (int t = 0; t < (kSwap ? 1 : kAwqPhaseTiles); ++t) {
       const float* src = part + ((size_t(phase) * kAwqPhaseTiles + t) * kGemmWarps + part_index) * kBlock + e;
 #pragma unroll
       for (int w = 0; w < 4; ++w) loaded[t][w] = src[size_t(w) * 4 * kBlock];
