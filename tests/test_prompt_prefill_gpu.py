@@ -108,6 +108,30 @@ def test_prompt_longer_than_one_segment(cuda, package):
         assert float(np.sqrt(((fa - fb) ** 2).mean())) <= 5e-3 * max(1.0, float(np.abs(fb).max()))
 
 
+def test_prompt_that_fills_the_cache_exactly_and_one_that_does_not_fit(cuda, package):
+    """Maximum sizes: a prompt of exactly `capacity` rows (one full segment of 2048) is taken and leaves no room for a
+    verify step; one row more is refused before any write, and the history stays."""
+    torch, syn, abi = cuda, package.synthetic, package.abi
+    shape = shapes(package)["qwen3_awq"]
+    model = package.Model(shape, syn.make_model(shape, seed=6, vary_norms=True))
+    session, narrow = model.new_session(2048, graph=True), model.new_session(2048, graph=True)
+    prompt = syn.make_prompt(33, 2048, shape.vocab_size)
+    session.prefill(prompt)
+    assert session.context_size() == 2048 == session.context_capacity()
+    narrow_prefill(torch, narrow, prompt, shape.vocab_size)
+    rms, worst = relative(syn.bf16_to_float(session.read_logits(1))[0], syn.bf16_to_float(narrow.read_logits(1))[0])
+    assert rms <= 1e-2 and worst <= 1.5e-2 * np.sqrt(shape.n_layers), (rms, worst)
+    kept = session.read_logits(1).copy()
+    with pytest.raises(abi.LengthError):
+        session.verify([1, 2, 3])
+    with pytest.raises(abi.LengthError):
+        session.prefill(syn.make_prompt(34, 2049, shape.vocab_size))
+    assert session.context_size() == 2048 and np.array_equal(session.read_logits(1), kept)
+    session.truncate(2040)
+    out = session.verify([1, 2, 3])
+    assert out.context == 2040 + out.emitted
+
+
 def test_speculative_decoder_after_long_prompt_equals_greedy(cuda, package):
     """The speculative loop's output after a long prompt is the target's own greedy continuation."""
     syn = package.synthetic
