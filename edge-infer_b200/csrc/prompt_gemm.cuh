@@ -130,8 +130,10 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
                                                          ~uintptr_t(1023));
   PromptShared* sh = reinterpret_cast<PromptShared*>(smem + size_t(kPromptStages) * kPromptStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kPromptFeatures, t0 = blockIdx.y * (kPromptTokens * kPromptTokenTiles);
-  const int token_tiles = min(kPromptTokenTiles, (p.M - t0 + kPromptTokens - 1) / kPromptTokens);
+  // p.prompt_tiles (1 or 2) token tiles per block: chosen on the host so that the grid's waves are well filled.
+  const int tiles_per_block = p.prompt_tiles == 1 ? 1 : kPromptTokenTiles;
+  const int n0 = blockIdx.x * kPromptFeatures, t0 = blockIdx.y * (kPromptTokens * tiles_per_block);
+  const int token_tiles = min(tiles_per_block, (p.M - t0 + kPromptTokens - 1) / kPromptTokens);
   // K slice of this block (blockIdx.z of p.ksplit): whole quantisation groups, i.e. pairs of K blocks.
   const int slice = blockIdx.z;
   const int pairs_total = p.K / (2 * kPromptBlockK);

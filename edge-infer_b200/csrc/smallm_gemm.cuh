@@ -55,6 +55,7 @@ struct GemmParams {
   int* best_index;        //             [grid, 16]
   int* status;            // optional device word; bit 2 is set if a bounded wait on a bulk copy gave up
   uint32_t wait_limit;    // polls before a bounded wait gives up (0: the kernel's default)
+  int prompt_tiles;       // prompt GEMM only: token tiles of 128 rows per block (0: chosen by the launch function)
   uint32_t fault_tx;      // test hook: bytes the first weight copy is expected to deliver beyond what it does,
                           // so that the bounded waits run out (0 in production)
 };
@@ -391,6 +392,8 @@ bool prompt_gemm_eligible(bool awq, int group_size, int N, int K, const void* x,
 // Uses p.x, x_stride, M (= T), K, N, the weight fields of its kind, bias, out, out_stride, epilogue, ksplit,
 // partial, status, wait_limit, fault_tx.
 int prompt_gemm_ksplit(int rows, int N, int K, int multiprocessors, size_t partial_bytes);
+// Token tiles per block (1 or 2) that fill the grid's waves best for this shape.
+int prompt_gemm_tiles(int rows, int N, int multiprocessors);
 void launch_prompt_gemm(bool awq, const GemmParams& p, cudaStream_t stream, bool pdl);
 
 
