@@ -18,7 +18,8 @@
 //     accumulate in tensor memory - 2 token tiles x 256 FP32 columns = all 512 columns - and commits the stage's
 //     `empty` barrier, which hands the stage back to the copy thread;
 //   * after the last K block warps 0-7 read the accumulators with tcgen05.ld (warp w: lanes 32 (w % 4) ..., token
-//     tile w / 4), add the bias in FP32, round once to BF16 and store - or, for a projection whose sum the
+//     tile w / 4), add the bias in FP32, round once to BF16 and store whole output rows through shared memory -
+//     or, for a projection whose sum the
 //     residual + norm kernel finishes, store FP32 partial sums, K split over blockIdx.z so that few token tiles
 //     still fill the SMs.
 // Rows beyond T and features beyond N are zero-filled by TMA and masked in the epilogue.
@@ -288,32 +289,65 @@ __global__ void __launch_bounds__(kPromptThreads, 1)
     tcgen05_fence_after();
     const int quarter = warp & 3, mt = warp >> 2;
     if (complete && mt < token_tiles) {
-      const int token = t0 + mt * kPromptTokens + quarter * 32 + lane;
-      bf16* out_row = p.out + size_t(token) * p.out_stride + n0;
+      // The accumulators come out of tensor memory one token per lane, which would make every store of a warp hit
+      // 32 different output rows. They go through shared memory instead (the ring's stages are free by now; a
+      // padded row pitch keeps both directions conflict-free), 128 columns at a time, and leave as whole rows:
+      // sixteen lanes write 256 contiguous bytes of a BF16 row (thirty-two lanes 512 bytes of an FP32 one).
+      const bool partial = p.epilogue == kEpiPartial;
+      constexpr int kPitch = 528;  // bytes per staged row: 512 of FP32 (or 256 of BF16) plus 16
+      unsigned char* staged = smem + size_t(warp) * 32 * kPitch;
+      const int first_token = t0 + mt * kPromptTokens + quarter * 32;
 #pragma unroll 1
-      for (int cb = 0; cb < kPromptFeatures / 16; ++cb) {
-        if (n0 + cb * 16 >= p.N) break;  // block-uniform
-        float v[16];
-        tmem_load16(tmem + (uint32_t(quarter * 32) << 16) + mt * kPromptFeatures + cb * 16, v);
-        if (token < p.M && p.epilogue == kEpiPartial) {
-          float* dst = p.partial + (size_t(slice) * p.M + token) * p.N + n0 + cb * 16;
+      for (int half = 0; half < 2; ++half) {
+        if (n0 + half * 128 >= p.N) break;  // block-uniform
+#pragma unroll 1
+        for (int cb = 0; cb < 8; ++cb) {
+          float v[16];
+          tmem_load16(tmem + (uint32_t(quarter * 32) << 16) + mt * kPromptFeatures + half * 128 + cb * 16, v);
+          if (partial) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else if (token < p.M) {
-          uint32_t packed[8];
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<float4*>(staged + lane * kPitch + cb * 64 + i * 16) =
+                  make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+            uint32_t packed[8];
+            const int column = n0 + half * 128 + cb * 16;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float a = v[2 * i], b = v[2 * i + 1];
-            if (p.bias) {
-              a += __bfloat162float(p.bias[n0 + cb * 16 + 2 * i]);
-              b += __bfloat162float(p.bias[n0 + cb * 16 + 2 * i + 1]);
+            for (int i = 0; i < 8; ++i) {
+              float a = v[2 * i], b = v[2 * i + 1];
+              if (p.bias && column + 2 * i + 1 < p.N) {
+                a += __bfloat162float(p.bias[column + 2 * i]);
+                b += __bfloat162float(p.bias[column + 2 * i + 1]);
+              }
+              packed[i] = pack_bf16(a, b);
             }
-            packed[i] = pack_bf16(a, b);
+            *reinterpret_cast<uint4*>(staged + lane * kPitch + cb * 32) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(staged + lane * kPitch + cb * 32 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
           }
-          *reinterpret_cast<uint4*>(out_row + cb * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(out_row + cb * 16 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
         }
+        __syncwarp();
+        if (partial) {
+          // One staged row (128 floats) per instruction.
+          const int column = n0 + half * 128 + lane * 4;
+#pragma unroll 4
+          for (int r = 0; r < 32; ++r) {
+            const int token = first_token + r;
+            if (token < p.M && column < p.N)
+              *reinterpret_cast<float4*>(p.partial + (size_t(slice) * p.M + token) * p.N + column) =
+                  *reinterpret_cast<const float4*>(staged + r * kPitch + lane * 16);
+          }
+        } else {
+          // Two staged rows (128 BF16 values each) per instruction.
+          const int column = n0 + half * 128 + (lane & 15) * 8;
+#pragma unroll 4
+          for (int r = lane >> 4; r < 32; r += 2) {
+            const int token = first_token + r;
+            if (token < p.M && column < p.N)
+              *reinterpret_cast<uint4*>(p.out + size_t(token) * p.out_stride + column) =
+                  *reinterpret_cast<const uint4*>(staged + r * kPitch + (lane & 15) * 16);
+          }
+        }
+        __syncwarp();
       }
     }
   }
