@@ -102,6 +102,29 @@ void for_row_groups(size_t rows, Launch&& body) {
 
 using namespace ei;
 
+namespace {
+// The prompt kernel for an operator call: K split over blocks when the caller's scratch allows it and the grid
+// would otherwise leave most SMs idle; the slices are added (with the bias, rounded once) by a second kernel.
+void run_prompt_operator(const ei_context* ctx, bool awq, GemmParams p, void* scratch, size_t scratch_bytes,
+                         cudaStream_t stream) {
+  const int ksplit = (scratch && p.N % 4 == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0)
+                         ? prompt_gemm_ksplit(p.M, p.N, p.K, ctx->multiprocessors, scratch_bytes) : 1;
+  if (ksplit < 2) {
+    launch_prompt_gemm(awq, p, stream, false);
+    return;
+  }
+  bf16* out = p.out;
+  const bf16* bias = p.bias;
+  p.epilogue = kEpiPartial;
+  p.ksplit = ksplit;
+  p.partial = static_cast<float*>(scratch);
+  launch_prompt_gemm(awq, p, stream, false);
+  splitk_store_kernel<<<std::min(ctx->multiprocessors * 8, (p.M * p.N + 255) / 256), 256, 0, stream>>>(
+      p.partial, ksplit, p.M, p.N, bias, out, p.out_stride);
+  check_launch();
+}
+}  // namespace
+
 extern "C" {
 
 const char* ei_last_error(void) { return g_last_error.c_str(); }
@@ -183,7 +206,9 @@ ei_status ei_prepare_awq_bf16(ei_view2 qweight, ei_view2 scales, ei_view2 zeros,
 
 size_t ei_linear_scratch_bytes(size_t rows, size_t input_features, size_t output_features) {
   (void)input_features;
-  // Worst case split of the input features over blocks: 16 FP32 partial copies of a 16-row group.
+  // Up to 32 rows: worst case split of the input features over blocks, 16 FP32 partial copies of a 16-row group.
+  // More rows (the prompt kernel): up to four K slices of all rows, used when the grid would otherwise be small.
+  if (rows > size_t(kPromptMinRows)) return size_t(4) * rows * output_features * sizeof(float);
   return size_t(16) * std::min<size_t>(rows, 16) * output_features * sizeof(float);
 }
 
@@ -208,7 +233,7 @@ ei_status ei_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_dense_w
       p.w = static_cast<const bf16*>(weight->data); p.ldw = weight->leading_dimension;
       p.bias = static_cast<const bf16*>(weight->bias);
       p.out = static_cast<bf16*>(output.data); p.out_stride = N;
-      launch_prompt_gemm(false, p, stream, false);
+      run_prompt_operator(ctx, false, p, scratch, scratch_bytes, stream);
       return;
     }
     for_row_groups(input.shape[0], [&](size_t first, size_t rows) {
@@ -271,7 +296,7 @@ ei_status ei_awq_linear_bf16(const ei_context* ctx, ei_view2 input, const ei_awq
       p.zero_stride = (K / 128 + 7) / 8;
       p.bias = static_cast<const bf16*>(weight->bias);
       p.out = static_cast<bf16*>(output.data); p.out_stride = N;
-      launch_prompt_gemm(true, p, stream, false);
+      run_prompt_operator(ctx, true, p, scratch, scratch_bytes, stream);
       return;
     }
     for_row_groups(input.shape[0], [&](size_t first, size_t rows) {

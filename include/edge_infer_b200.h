@@ -84,8 +84,9 @@ ei_status ei_prepare_dense_bf16(ei_view2 weight, ei_view1 bias, ei_dense_weight*
 /* ref: execution.hpp:58-64, execution.cu:285-298 prepare_awq<T>(qweight, scales, zeros, group, in, bias). */
 ei_status ei_prepare_awq_bf16(ei_view2 qweight, ei_view2 scales, ei_view2 zeros, size_t group_size,
                               size_t input_features, ei_view1 bias, ei_awq_weight* out);
-/* Bytes of caller-owned FP32 scratch the linear operators need for `rows` input rows (0 when the
- * shape needs no split over the input features). */
+/* Bytes of caller-owned FP32 scratch the linear operators can use for `rows` input rows: partial sums of the
+ * slices when the input features are split over blocks. Without scratch the operators still work; shapes that
+ * need the split then take a slower kernel (<= 32 rows) or leave SMs idle (more rows, few output features). */
 size_t ei_linear_scratch_bytes(size_t rows, size_t input_features, size_t output_features);
 /* ref: execution.hpp:65-67, execution.cu:299-324 linear<T>: out[rows,N] = round_bf16(x W + bias), FP32
  * accumulation, bias added before the single rounding. rows <= 16 takes the streaming kernel;

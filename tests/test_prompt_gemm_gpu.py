@@ -66,6 +66,14 @@ def test_awq_prompt_gemm(cuda, package, oracle, ctx, rows, nk):
     got, other = syn.bf16_to_float(to_host(out)), syn.bf16_to_float(to_host(narrow))
     assert np.all(np.abs(got - other) <= tolerance(other))
     assert np.mean(got == other) > 0.97
+    # With caller scratch the kernel may split K over blocks (FP32 slices added by a second kernel).
+    wide_scratch = torch.empty(ops.linear_scratch_bytes(rows, k, n), dtype=torch.uint8, device="cuda")
+    split = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.awq_linear(ctx, dx, weight, split, wide_scratch)
+    torch.cuda.synchronize()
+    with_split = syn.bf16_to_float(to_host(split))
+    assert np.all(np.abs(with_split - other) <= tolerance(other))
+    assert np.mean(with_split == other) > 0.97
     cols = np.random.default_rng(n + k).choice(n, size=min(n, 128), replace=False)
     pick = np.random.default_rng(rows).choice(rows, size=min(rows, 64), replace=False)
     dense = syn.awq_dequantize(q[cols], s[cols], z[cols], k)
