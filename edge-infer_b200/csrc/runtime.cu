@@ -189,11 +189,6 @@ struct Builder {
       throw std::invalid_argument("Qwen3 weight shape mismatch: " + name);
     return static_cast<const bf16*>(place(s->dense->data, width * 2));
   }
-  const bf16* optional_vector(const std::string& name, size_t width) {
-    const Source* s = find(name);
-    if (!s || !s->dense) return nullptr;
-    return vector(name, width);
-  }
 
   // Concatenates projections that share their input along the output axis (rows of the N-major
   // layout), so that one launch streams them all.
