@@ -377,6 +377,64 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttentionPar
   *reinterpret_cast<uint2*>(dst) = packed;
 }
 
+// The merge for a wide batch: one WARP per (session, row, head) and no block-wide barrier, four per block. With
+// thousands of (row, head) slots a block per slot costs one launch wave after another of blocks that each wait on
+// two trips to memory; here a warp requests all of its slot's partials (lane l owns outputs 4l .. 4l + 3) before it
+// combines them in split order.
+__global__ void __launch_bounds__(128) attention_merge_wide_kernel(const AttentionParams p) {
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int slots = p.rows * p.heads;
+  const int slot_global = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (slot_global >= slots * p.sessions) return;
+  const int session = slot_global / slots, slot = slot_global - session * slots;
+  const SessionSlot owner = p.slots[session];
+  const int offset = owner.control->context, length = offset + p.rows;
+  if (offset < 0 || length > owner.capacity) return;
+  const int splits = min(64, (length + p.chunk - 1) / p.chunk);
+  const float* base = p.scratch + size_t(session) * p.scratch_stride + size_t(slot) * kPartial;
+  const size_t step = size_t(slots) * kPartial;
+  float maximum = -INFINITY;
+  for (int s = lane; s < splits; s += 32) maximum = fmaxf(maximum, base[s * step + 128]);
+  maximum = warp_max(maximum);
+  float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float denominator = 0.0f;
+  for (int first = 0; first < splits; first += 8) {
+    float4 values[8];
+    float m[8], l[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int s = first + i;
+      values[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      m[i] = -INFINITY;
+      l[i] = 0.0f;
+      if (s < splits) {
+        const float* src = base + s * step;
+        values[i] = *reinterpret_cast<const float4*>(src + 4 * lane);
+        m[i] = src[128];
+        l[i] = src[129];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float weight = m[i] == -INFINITY ? 0.0f : __expf(m[i] - maximum);  // a split with nothing visible counts 0
+      sum.x = fmaf(values[i].x, weight, sum.x);
+      sum.y = fmaf(values[i].y, weight, sum.y);
+      sum.z = fmaf(values[i].z, weight, sum.z);
+      sum.w = fmaf(values[i].w, weight, sum.w);
+      denominator = fmaf(l[i], weight, denominator);
+    }
+  }
+  const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
+  const int row = slot / p.heads, head = slot - row * p.heads;
+  bf16* dst = p.out + (size_t(session) * p.rows + row) * p.out_stride + size_t(head) * kDim + 4 * lane;
+  uint2 packed;
+  packed.x = pack_bf16(sum.x * inverse, sum.y * inverse);
+  packed.y = pack_bf16(sum.z * inverse, sum.w * inverse);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
 }  // namespace
 
 int attention_chunk_for(size_t kv_length) {
@@ -438,7 +496,10 @@ void launch_verify_attention(const AttentionParams& p, cudaStream_t stream, bool
   const unsigned sessions = q.slots ? unsigned(q.sessions) : 1u;
   launch(verify_attention_kernel<false>, dim3(q.kv_heads, q.max_splits, sessions), dim3(warps * 32), kAttentionShared,
          stream, pdl, q);
-  launch(attention_merge_kernel, dim3(q.rows * q.heads, sessions), dim3(128), 0, stream, pdl, q);
+  if (q.slots)
+    launch(attention_merge_wide_kernel, dim3((q.rows * q.heads * q.sessions + 3) / 4), dim3(128), 0, stream, pdl, q);
+  else
+    launch(attention_merge_kernel, dim3(q.rows * q.heads, sessions), dim3(128), 0, stream, pdl, q);
 }
 
 void launch_prompt_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
