@@ -190,3 +190,53 @@ def test_full_shape_verify_against_reference_cuda_path(cuda, package, oracle, na
     device_tensors = syn.make_device_model(shape, seed=0)
     host_tensors = host_copy(cuda, device_tensors)
     run_against_reference(cuda, package, oracle, name, shape, device_tensors, host_tensors)
+
+
+@pytest.mark.parametrize("name", ["qwen3_awq", "qwen25_awq_bias"])
+def test_wide_batch_against_reference_cuda_path(cuda, package, oracle, name):
+    """Twenty sessions verified in one forward (the wide form of ei_batch_verify, projections on the prompt GEMM)
+    against the reference CUDA path run once per session on the same prompts and drafts: every row whose reference
+    top-2 gap exceeds twice the configuration's element bound must give the reference's greedy token, and a session
+    whose emitted prefix is decisive must have the reference's accept length."""
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref not built")
+    syn = package.synthetic
+    shape = small_shapes(package)[name]
+    rows, p, _, _, capacity, _, element_bound, _, _ = BOUNDS[name]
+    tensors = syn.make_model(shape, seed=12, vary_norms=True)
+    model = package.Model(shape, tensors)
+    reference = oracle.ReferenceCuda(shape, tensors, capacity)
+    count = 20
+    sessions = [model.new_session(capacity, graph=True) for _ in range(count)]
+    prompts = [syn.make_prompt(500 + j, 17 + (13 * j) % 90, shape.vocab_size) for j in range(count)]
+    rng = np.random.default_rng(3)
+    inputs, expected = [], []
+    for session, prompt in zip(sessions, prompts):
+        session.prefill(prompt)
+        reference.resize(0)
+        _, greedy = reference.forward(prompt)
+        pending, continuation, token = int(greedy[-1]), [], int(greedy[-1])
+        length = reference.size()
+        for _ in range(rows - 1):
+            token = int(reference.forward([token])[1][0])
+            continuation.append(token)
+        reference.resize(length)
+        drafts = np.array(continuation, dtype=np.uint32)
+        drafts = np.where(rng.random(len(drafts)) < p, rng.integers(0, shape.vocab_size, len(drafts)), drafts)
+        tokens = np.concatenate([[pending], drafts]).astype(np.uint32)
+        ref_logits, ref_greedy = reference.forward(tokens)
+        inputs.append([int(t) for t in tokens])
+        expected.append((ref_logits, ref_greedy, oracle.accept(tokens, ref_greedy)))
+    outs = package.runtime.SessionBatch(sessions).verify(inputs)
+    decisive_rows = equal_rows = 0
+    for out, (ref_logits, ref_greedy, emitted) in zip(outs, expected):
+        decisive = oracle.top2_gap(ref_logits) > 2 * element_bound * float(np.abs(ref_logits).max())
+        for r in range(rows):
+            equal_rows += out.targets[r] == int(ref_greedy[r])
+            if decisive[r]:
+                decisive_rows += 1
+                assert out.targets[r] == int(ref_greedy[r])
+        if decisive[:emitted].all():
+            assert out.emitted == emitted
+    assert decisive_rows >= count                      # not vacuous
+    assert equal_rows >= 0.9 * count * rows
