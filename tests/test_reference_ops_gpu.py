@@ -111,7 +111,7 @@ def test_rope_and_store_kv_equal_reference_kernels(cuda, package, ref, ctx):
     assert torch.equal(bits(cache_a), bits(cache_b))
 
 
-@pytest.mark.parametrize("rows", [2, 5, 9, 16])
+@pytest.mark.parametrize("rows", [2, 5, 9, 16, 300])       # 300: the tcgen05 prompt kernel against the reference's GEMM
 @pytest.mark.parametrize("nk_bias", [((4096, 4096), False), ((1024, 4096), False), ((4096, 12288), False),
                                      ((512, 3584), True), ((3584, 18944), False)])
 def test_awq_linear_against_reference_kernel(cuda, package, ref, ctx, rows, nk_bias):
@@ -135,7 +135,7 @@ def test_awq_linear_against_reference_kernel(cuda, package, ref, ctx, rows, nk_b
     assert np.mean(a == r) > 0.9
 
 
-@pytest.mark.parametrize("rows", [1, 9, 16])
+@pytest.mark.parametrize("rows", [1, 9, 16, 300])
 @pytest.mark.parametrize("nk", [(8192, 4096), (2048, 2048), (1024, 6144)])
 def test_dense_linear_against_reference_cublas(cuda, package, ref, ctx, rows, nk):
     torch, ops = cuda, package.operators
